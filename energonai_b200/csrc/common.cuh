@@ -1,0 +1,84 @@
+// Shared helpers for the energon_b200 kernels: error reporting for the C ABI, dtype traits,
+// 16-byte vector access, warp/block reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/energon_b200.h"
+
+namespace eb {
+
+// ---- error reporting (thread-local message behind eb_last_error) -----------------------
+int fail(int code, const char *fmt, ...);
+int check_launch(const char *what);   // cudaPeekAtLastError -> EB_ECUDA
+
+#define EB_REQUIRE(cond, ...)                         \
+  do {                                                \
+    if (!(cond)) return ::eb::fail(EB_EINVAL, __VA_ARGS__); \
+  } while (0)
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int dtype_size(int dtype) { return dtype == EB_F32 ? 4 : 2; }
+inline bool dtype_ok(int dtype) { return dtype == EB_F32 || dtype == EB_F16 || dtype == EB_BF16; }
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+int sm_count();   // multiprocessors of the current device (cached per device)
+
+// ---- dtype conversion ---------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// A 16-byte vector of T (4 floats or 8 halves) with fp32 unpack/pack.
+template <typename T> struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  uint4 raw;
+  __device__ __forceinline__ void load(const T *p) { raw = *reinterpret_cast<const uint4 *>(p); }
+  __device__ __forceinline__ void store(T *p) const { *reinterpret_cast<uint4 *>(p) = raw; }
+  __device__ __forceinline__ void unpack(float (&f)[N]) const {
+    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] = to_f32<T>(e[i]);
+  }
+  __device__ __forceinline__ void pack(const float (&f)[N]) {
+    T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < N; ++i) e[i] = from_f32<T>(f[i]);
+  }
+};
+
+// ---- reductions ---------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a CTA of THREADS threads (multiple of 32); every thread gets the result.
+// `scratch` must hold THREADS/32 floats; safe to call repeatedly with the same scratch.
+template <int THREADS> __device__ __forceinline__ float block_sum(float v, float *scratch) {
+  if (THREADS == 32) return warp_sum(v);
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();   // previous use of scratch is complete
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = lane < THREADS / 32 ? scratch[lane] : 0.f;
+  return warp_sum(r);
+}
+
+}  // namespace eb

@@ -1,0 +1,198 @@
+// LayerNorm forward with optional fused residual / bias add.
+//
+// One CTA of 128 threads per row.  The row (after the optional adds) is loaded once in
+// 16-byte vectors into fp32 registers; mean and the centred second moment are each one
+// block reduction over the register copy (two-pass, so no cancellation), and the output is
+// written once.  HBM traffic is therefore the algorithmic minimum: one read of every input
+// operand and one write of every output.  Rows that do not fit the register budget, or that
+// are not 16-byte aligned, take a three-pass variant that re-reads the operands.
+#include "common.cuh"
+
+namespace eb {
+namespace {
+
+constexpr int kThreads = 128;
+
+template <typename T, int VEC> struct alignas(sizeof(T) * VEC > 16 ? 16 : sizeof(T) * VEC) Pack { T e[VEC]; };
+
+template <typename Tin, typename Tout, int MAXV>
+__global__ void __launch_bounds__(kThreads)
+ln_cached_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restrict__ invvar,
+                 const Tin *__restrict__ x, const Tin *__restrict__ residual, const Tin *__restrict__ bias,
+                 Tin *__restrict__ sum_out, const Tout *__restrict__ gamma, const Tout *__restrict__ beta,
+                 long long n1, int n2, float eps) {
+  constexpr int VEC = 16 / sizeof(Tin);
+  using PI = Pack<Tin, VEC>;
+  using PO = Pack<Tout, VEC>;
+  __shared__ float scratch[kThreads / 32];
+  const int packs = n2 / VEC;
+  const float inv_n = 1.f / (float)n2;
+  for (long long row = blockIdx.x; row < n1; row += gridDim.x) {
+    const PI *xr = reinterpret_cast<const PI *>(x + row * n2);
+    const PI *rr = residual ? reinterpret_cast<const PI *>(residual + row * n2) : nullptr;
+    float v[MAXV][VEC];
+    float s = 0.f;
+#pragma unroll
+    for (int t = 0; t < MAXV; ++t) {
+      const int p = threadIdx.x + t * kThreads;
+      if (p < packs) {
+        PI a = xr[p];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v[t][e] = to_f32<Tin>(a.e[e]);
+        if (rr) {
+          PI r = rr[p];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) v[t][e] += to_f32<Tin>(r.e[e]);
+        }
+        if (bias) {
+          PI bb = reinterpret_cast<const PI *>(bias)[p];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) v[t][e] += to_f32<Tin>(bb.e[e]);
+        }
+        if (sum_out) {
+          // the residual stream continues in the input precision: normalise what is stored
+          PI o;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) { o.e[e] = from_f32<Tin>(v[t][e]); v[t][e] = to_f32<Tin>(o.e[e]); }
+          reinterpret_cast<PI *>(sum_out + row * n2)[p] = o;
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) s += v[t][e];
+      }
+    }
+    const float mu = block_sum<kThreads>(s, scratch) * inv_n;
+    float q = 0.f;
+#pragma unroll
+    for (int t = 0; t < MAXV; ++t) {
+      const int p = threadIdx.x + t * kThreads;
+      if (p < packs) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { const float d = v[t][e] - mu; q += d * d; }
+      }
+    }
+    const float var = block_sum<kThreads>(q, scratch) * inv_n;
+    const float iv = rsqrtf(var + eps);
+    PO *yr = reinterpret_cast<PO *>(y + row * n2);
+#pragma unroll
+    for (int t = 0; t < MAXV; ++t) {
+      const int p = threadIdx.x + t * kThreads;
+      if (p < packs) {
+        PO o;
+        if (gamma) {
+          PO g = reinterpret_cast<const PO *>(gamma)[p], bt = reinterpret_cast<const PO *>(beta)[p];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            o.e[e] = from_f32<Tout>(to_f32<Tout>(g.e[e]) * ((v[t][e] - mu) * iv) + to_f32<Tout>(bt.e[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) o.e[e] = from_f32<Tout>((v[t][e] - mu) * iv);
+        }
+        yr[p] = o;
+      }
+    }
+    if (threadIdx.x == 0) {
+      if (mean) mean[row] = mu;
+      if (invvar) invvar[row] = iv;
+    }
+  }
+}
+
+// Any n2 / alignment: element-wise, operands re-read in each of the three passes.
+template <typename Tin, typename Tout>
+__global__ void __launch_bounds__(kThreads)
+ln_generic_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restrict__ invvar,
+                  const Tin *__restrict__ x, const Tin *__restrict__ residual, const Tin *__restrict__ bias,
+                  Tin *__restrict__ sum_out, const Tout *__restrict__ gamma, const Tout *__restrict__ beta,
+                  long long n1, int n2, float eps) {
+  __shared__ float scratch[kThreads / 32];
+  const float inv_n = 1.f / (float)n2;
+  for (long long row = blockIdx.x; row < n1; row += gridDim.x) {
+    const Tin *xr = x + row * n2;
+    const Tin *rr = residual ? residual + row * n2 : nullptr;
+    auto value = [&](int i) {
+      float t = to_f32<Tin>(xr[i]);
+      if (rr) t += to_f32<Tin>(rr[i]);
+      if (bias) t += to_f32<Tin>(bias[i]);
+      return sum_out ? to_f32<Tin>(from_f32<Tin>(t)) : t;
+    };
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n2; i += kThreads) s += value(i);
+    const float mu = block_sum<kThreads>(s, scratch) * inv_n;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < n2; i += kThreads) { const float d = value(i) - mu; q += d * d; }
+    const float iv = rsqrtf(block_sum<kThreads>(q, scratch) * inv_n + eps);
+    for (int i = threadIdx.x; i < n2; i += kThreads) {
+      const float t = value(i);
+      float o = (t - mu) * iv;
+      if (gamma) o = to_f32<Tout>(gamma[i]) * o + to_f32<Tout>(beta[i]);
+      y[row * n2 + i] = from_f32<Tout>(o);
+    }
+    if (sum_out) {
+      __syncthreads();   // all reads of x/residual for this row are done (sum_out may alias them)
+      for (int i = threadIdx.x; i < n2; i += kThreads) {
+        float t = to_f32<Tin>(xr[i]);
+        if (rr) t += to_f32<Tin>(rr[i]);
+        if (bias) t += to_f32<Tin>(bias[i]);
+        sum_out[row * n2 + i] = from_f32<Tin>(t);
+      }
+    }
+    if (threadIdx.x == 0) {
+      if (mean) mean[row] = mu;
+      if (invvar) invvar[row] = iv;
+    }
+  }
+}
+
+template <typename Tin, typename Tout>
+int launch_ln(void *y, float *mean, float *invvar, const void *x, const void *residual, const void *bias,
+              void *sum_out, const void *gamma, const void *beta, long long n1, int n2, float eps, cudaStream_t st) {
+  constexpr int VEC = 16 / sizeof(Tin);
+  const long long cap = (long long)sm_count() * 16;
+  const int grid = (int)(n1 < cap ? n1 : cap);
+  const bool vec_ok = n2 % VEC == 0 && aligned16(x) && aligned16(y) && aligned16(residual) && aligned16(bias) &&
+                      aligned16(sum_out) && aligned16(gamma) && aligned16(beta) &&
+                      ((size_t)n2 * sizeof(Tout)) % 16 == 0;
+  const int packs = n2 / VEC;
+#define EB_LN_ARGS (Tout *)y, mean, invvar, (const Tin *)x, (const Tin *)residual, (const Tin *)bias, (Tin *)sum_out, \
+                   (const Tout *)gamma, (const Tout *)beta, n1, n2, eps
+  if (vec_ok && packs <= kThreads * 16) {
+    const int need = (packs + kThreads - 1) / kThreads;
+    if (need <= 1) ln_cached_kernel<Tin, Tout, 1><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
+    else if (need <= 2) ln_cached_kernel<Tin, Tout, 2><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
+    else if (need <= 4) ln_cached_kernel<Tin, Tout, 4><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
+    else if (need <= 8) ln_cached_kernel<Tin, Tout, 8><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
+    else ln_cached_kernel<Tin, Tout, 16><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
+  } else {
+    ln_generic_kernel<Tin, Tout><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
+  }
+#undef EB_LN_ARGS
+  return check_launch("layer_norm_fwd");
+}
+
+template <typename Tin>
+int dispatch_out(int out_dtype, void *y, float *mean, float *invvar, const void *x, const void *residual,
+                 const void *bias, void *sum_out, const void *gamma, const void *beta, long long n1, int n2, float eps,
+                 cudaStream_t st) {
+  if (out_dtype == EB_F32) return launch_ln<Tin, float>(y, mean, invvar, x, residual, bias, sum_out, gamma, beta, n1, n2, eps, st);
+  if (out_dtype == EB_F16) return launch_ln<Tin, __half>(y, mean, invvar, x, residual, bias, sum_out, gamma, beta, n1, n2, eps, st);
+  return launch_ln<Tin, __nv_bfloat16>(y, mean, invvar, x, residual, bias, sum_out, gamma, beta, n1, n2, eps, st);
+}
+
+}  // namespace
+}  // namespace eb
+
+extern "C" int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x, const void *residual,
+                                 const void *bias, void *sum_out, const void *gamma, const void *beta, int64_t n1,
+                                 int n2, double eps, int in_dtype, int out_dtype, void *stream) {
+  using namespace eb;
+  EB_REQUIRE(dtype_ok(in_dtype) && dtype_ok(out_dtype), "layer_norm_fwd: bad dtype %d/%d", in_dtype, out_dtype);
+  EB_REQUIRE(n1 >= 0 && n2 >= 0, "layer_norm_fwd: negative size");
+  if (n1 == 0 || n2 == 0) return EB_OK;
+  EB_REQUIRE(y && x, "layer_norm_fwd: null input or output");
+  EB_REQUIRE((gamma == nullptr) == (beta == nullptr), "layer_norm_fwd: gamma and beta must both be given or both be NULL");
+  cudaStream_t st = as_stream(stream);
+  const float e = (float)eps;
+  if (in_dtype == EB_F32) return dispatch_out<float>(out_dtype, y, mean, invvar, x, residual, bias, sum_out, gamma, beta, n1, n2, e, st);
+  if (in_dtype == EB_F16) return dispatch_out<__half>(out_dtype, y, mean, invvar, x, residual, bias, sum_out, gamma, beta, n1, n2, e, st);
+  return dispatch_out<__nv_bfloat16>(out_dtype, y, mean, invvar, x, residual, bias, sum_out, gamma, beta, n1, n2, e, st);
+}

@@ -1,0 +1,158 @@
+// In-place masked softmax over attention scores [batch, heads, S, S].
+//
+// One warp per query row.  The visible prefix of the row (keys j <= i under the causal
+// mask, j < real_len under the key-length mask) is loaded once in 16-byte vectors and kept
+// in registers, reduced with warp shuffles (max, then sum of exp), and the whole row is
+// written back once: probabilities for visible keys, exact zeros for masked keys.  Only
+// the visible prefix is ever read, so a causal row i costs (i+1) reads + S writes.
+// Rows longer than the register budget take a variant that re-reads the row from memory.
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace eb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+template <typename T, int VEC> struct alignas(sizeof(T) * VEC > 16 ? 16 : sizeof(T) * VEC) Pack { T e[VEC]; };
+
+// VPL = packs cached per lane (0: no caching, re-read).
+template <typename T, int VEC, int VPL>
+__global__ void __launch_bounds__(kThreads)
+softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int B, int S, int H, int flags,
+               float scale) {
+  using P = Pack<T, VEC>;
+  const int lane = threadIdx.x & 31;
+  const long long rows = (long long)B * H * S;
+  const long long warp0 = (long long)blockIdx.x * kWarps + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * kWarps;
+  const int packs_row = S / VEC;   // S % VEC == 0 on this path
+  for (long long row = warp0; row < rows; row += nwarps) {
+    const int i = (int)(row % S);
+    const int b = (int)(row / ((long long)H * S));
+    int len = real_len[b];
+    len = len < 0 ? 0 : (len > S ? S : len);
+    if (i >= len && !(flags & EB_SM_ALLROWS)) continue;
+    int nvis = S;
+    if (flags & EB_SM_CAUSAL) nvis = min(nvis, i + 1);
+    if (flags & EB_SM_KEYLEN) nvis = min(nvis, len);
+    P *rp = reinterpret_cast<P *>(scores + row * S);
+    const int packs_vis = (nvis + VEC - 1) / VEC;
+
+    if (VPL > 0) {
+      P cache[VPL > 0 ? VPL : 1];
+      float mx = -FLT_MAX;
+#pragma unroll
+      for (int t = 0; t < VPL; ++t) {
+        const int v = lane + 32 * t;
+        if (v < packs_vis) {
+          cache[t] = rp[v];
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            if (v * VEC + e < nvis) mx = fmaxf(mx, to_f32<T>(cache[t].e[e]) * scale);
+        }
+      }
+      mx = warp_max(mx);
+      float sum = 0.f;
+      float ex[VPL > 0 ? VPL : 1][VEC];
+#pragma unroll
+      for (int t = 0; t < VPL; ++t) {
+        const int v = lane + 32 * t;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float p = 0.f;
+          if (v < packs_vis && v * VEC + e < nvis) p = __expf(to_f32<T>(cache[t].e[e]) * scale - mx);
+          ex[t][e] = p;
+          sum += p;
+        }
+      }
+      sum = warp_sum(sum);
+      const float inv = sum > 0.f ? 1.f / sum : 0.f;
+#pragma unroll
+      for (int t = 0; t < VPL; ++t) {
+        const int v = lane + 32 * t;
+        if (v < packs_row) {
+          P out;
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) out.e[e] = from_f32<T>(ex[t][e] * inv);
+          rp[v] = out;
+        }
+      }
+    } else {
+      float mx = -FLT_MAX;
+      for (int v = lane; v < packs_vis; v += 32) {
+        P c = rp[v];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          if (v * VEC + e < nvis) mx = fmaxf(mx, to_f32<T>(c.e[e]) * scale);
+      }
+      mx = warp_max(mx);
+      float sum = 0.f;
+      for (int v = lane; v < packs_vis; v += 32) {
+        P c = rp[v];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          if (v * VEC + e < nvis) sum += __expf(to_f32<T>(c.e[e]) * scale - mx);
+      }
+      sum = warp_sum(sum);
+      const float inv = sum > 0.f ? 1.f / sum : 0.f;
+      for (int v = lane; v < packs_row; v += 32) {
+        P c, out;
+        if (v < packs_vis) c = rp[v];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float p = 0.f;
+          if (v < packs_vis && v * VEC + e < nvis) p = __expf(to_f32<T>(c.e[e]) * scale - mx) * inv;
+          out.e[e] = from_f32<T>(p);
+        }
+        rp[v] = out;
+      }
+    }
+  }
+}
+
+template <typename T>
+int launch_softmax(void *scores, const int32_t *real_len, int B, int S, int H, int flags, float scale,
+                   cudaStream_t st) {
+  const long long rows = (long long)B * H * S;
+  long long g = (rows + kWarps - 1) / kWarps;
+  const long long cap = (long long)sm_count() * 32;
+  const int grid = (int)(g < cap ? g : cap);
+  constexpr int N = 16 / sizeof(T);
+  T *p = reinterpret_cast<T *>(scores);
+#define EB_SM_LAUNCH(VEC, VPL) \
+  softmax_kernel<T, VEC, VPL><<<grid, kThreads, 0, st>>>(p, real_len, B, S, H, flags, scale)
+  if (S % N == 0 && aligned16(scores)) {
+    const int packs = S / N;
+    if (packs <= 32) EB_SM_LAUNCH(N, 1);
+    else if (packs <= 64) EB_SM_LAUNCH(N, 2);
+    else if (packs <= 128) EB_SM_LAUNCH(N, 4);
+    else if (packs <= 256) EB_SM_LAUNCH(N, 8);
+    else EB_SM_LAUNCH(N, 0);
+  } else {
+    if (S <= 32) EB_SM_LAUNCH(1, 1);
+    else if (S <= 128) EB_SM_LAUNCH(1, 4);
+    else if (S <= 512) EB_SM_LAUNCH(1, 16);
+    else EB_SM_LAUNCH(1, 0);
+  }
+#undef EB_SM_LAUNCH
+  return check_launch("scale_mask_softmax");
+}
+
+}  // namespace
+}  // namespace eb
+
+extern "C" int eb_scale_mask_softmax(void *scores, const int32_t *real_seq_len, int batch, int seq_len, int head_num,
+                                     int dtype, int flags, float scale, void *stream) {
+  using namespace eb;
+  EB_REQUIRE(dtype_ok(dtype), "scale_mask_softmax: bad dtype %d", dtype);
+  EB_REQUIRE(batch >= 0 && seq_len >= 0 && head_num >= 0, "scale_mask_softmax: negative size");
+  EB_REQUIRE((flags & ~7) == 0, "scale_mask_softmax: unknown flag bits 0x%x", flags);
+  if ((long long)batch * seq_len * head_num == 0) return EB_OK;
+  EB_REQUIRE(scores && real_seq_len, "scale_mask_softmax: null pointer");
+  cudaStream_t st = as_stream(stream);
+  if (dtype == EB_F32) return launch_softmax<float>(scores, real_seq_len, batch, seq_len, head_num, flags, scale, st);
+  if (dtype == EB_F16) return launch_softmax<__half>(scores, real_seq_len, batch, seq_len, head_num, flags, scale, st);
+  return launch_softmax<__nv_bfloat16>(scores, real_seq_len, batch, seq_len, head_num, flags, scale, st);
+}

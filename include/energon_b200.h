@@ -1,0 +1,138 @@
+/*
+ * energon_b200 — C ABI of the B200 (sm_100a) implementation of EnergonAI's tensor-parallel
+ * transformer layer forward.
+ *
+ * Conventions (all entry points):
+ *   - plain pointers and sizes only; every tensor is allocated by the caller and must be
+ *     device memory of the current CUDA device, contiguous in the stated layout;
+ *   - `dtype` is one of EB_F32 / EB_F16 / EB_BF16;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); all work
+ *     is enqueued on it, nothing synchronises the device;
+ *   - the return value is EB_OK or a negative EB_E* code; on failure eb_last_error() returns
+ *     a thread-local human-readable message.  Nothing throws, exits or prints.
+ *
+ * Each declaration cites the reference interface it replaces (path inside the EnergonAI
+ * repository : line).
+ */
+#ifndef ENERGON_B200_H
+#define ENERGON_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define EB_API __attribute__((visibility("default")))
+#else
+#define EB_API
+#endif
+
+#define EB_OK 0
+#define EB_EINVAL (-1)       /* bad argument (null pointer, size, alignment, dtype)          */
+#define EB_ECUDA (-2)        /* the CUDA runtime / driver reported an error at launch        */
+#define EB_EUNSUPPORTED (-3) /* valid request outside what the kernels implement            */
+#define EB_ETIMEDOUT (-4)    /* a bounded device-side wait expired (see eb_device_status)    */
+#define EB_ELIMIT (-5)       /* request exceeds a documented fixed capacity                 */
+
+#define EB_F32 0
+#define EB_F16 1
+#define EB_BF16 2
+
+/* activation codes for eb_gemm */
+#define EB_ACT_NONE 0
+#define EB_ACT_RELU 1
+#define EB_ACT_GELU_TANH 2 /* energonai/model/model_factory.py:32-35 (gelu_impl)            */
+#define EB_ACT_GELU_ERF 3  /* torch.nn.functional.gelu                                      */
+
+/* flags for eb_scale_mask_softmax */
+#define EB_SM_CAUSAL 1  /* keys j > query i are masked to exactly 0 (reference behaviour)    */
+#define EB_SM_KEYLEN 2  /* keys j >= real_seq_len[b] are masked to exactly 0                 */
+#define EB_SM_ALLROWS 4 /* also rewrite query rows i >= real_seq_len[b] (reference skips them) */
+
+EB_API int eb_version(void);
+EB_API const char *eb_last_error(void);
+
+/* ---- padding offsets and (un)padding copies ------------------------------------------ */
+
+/* Replaces ft_build_padding_offsets_wrapper
+ * (energonai/kernel/cuda_native/csrc/transpose_pad_fusion_wrapper.cpp:93-104, kernel
+ * transpose_pad_fusion_kernel.cu:112-131).  seq_lens[batch] (each 0..max_seq_len);
+ * valid_word_num[0] = sum of lengths; tmp_mask_offset[k], k < sum, = number of padding slots
+ * before valid token k in the [batch, max_seq_len] layout.  tmp_mask_offset must hold at
+ * least sum(seq_lens) entries (batch*max_seq_len always suffices).  Entries beyond the sum
+ * are not written. */
+EB_API int eb_build_padding_offsets(const int32_t *seq_lens, int batch, int max_seq_len, int32_t *valid_word_num,
+                             int32_t *tmp_mask_offset, void *stream);
+
+/* Replaces ft_remove_padding_wrapper (transpose_pad_fusion_wrapper.cpp:113-140, kernel
+ * transpose_pad_fusion_kernel.cu:142-155): tgt[k,:] = src[k + off[k],:] for k < valid, and
+ * mask_offset[k] = tmp_mask_offset[k].  src [batch*max_seq_len, n], tgt [valid, n]. */
+EB_API int eb_remove_padding(const void *src, void *tgt, const int32_t *tmp_mask_offset, int32_t *mask_offset, int valid,
+                      int n, int dtype, void *stream);
+
+/* Replaces ft_rebuild_padding_wrapper (transpose_pad_fusion_wrapper.cpp:147-172, kernel
+ * transpose_pad_fusion_kernel.cu:178-190): tgt[k + off[k],:] = src[k,:].  The reference
+ * scatters into a freshly zeroed tensor; here the same kernel writes the zero rows
+ * (zero_fill != 0), so tgt [batch*max_seq_len, n] may be uninitialised memory. */
+EB_API int eb_rebuild_padding(const void *src, void *tgt, const int32_t *mask_offset, int valid, int n, int batch,
+                       int max_seq_len, int dtype, int zero_fill, void *stream);
+
+/* Replaces ft_transpose_rebuild_padding_wrapper (transpose_pad_fusion_wrapper.cpp:181-209,
+ * kernel transpose_pad_fusion_kernel.cu:213-236): packed Q,K,V [valid, head_num,
+ * size_per_head] -> q_buf,k_buf,v_buf [batch, head_num, seq_len, size_per_head].  With
+ * zero_fill == 0 rows of padding tokens are left untouched, as in the reference (whose
+ * callers pre-zero the buffers); with zero_fill != 0 they are written as zeros. */
+EB_API int eb_transpose_rebuild_padding(const void *Q, const void *K, const void *V, void *q_buf, void *k_buf, void *v_buf,
+                                 int batch, int seq_len, int head_num, int size_per_head, int valid,
+                                 const int32_t *mask_offset, int dtype, int zero_fill, void *stream);
+
+/* Replaces ft_transpose_remove_padding_wrapper (transpose_pad_fusion_wrapper.cpp:218-244,
+ * kernel transpose_pad_fusion_kernel.cu:268-289): src [batch, head_num, seq_len,
+ * size_per_head] -> dst [valid, head_num*size_per_head]. */
+EB_API int eb_transpose_remove_padding(const void *src, void *dst, int valid, int batch, int seq_len, int head_num,
+                                int size_per_head, const int32_t *mask_offset, int dtype, void *stream);
+
+/* Replaces transpose_pad_wrapper (transpose_pad_fusion_wrapper.cpp:33-57, kernel
+ * transpose_pad_fusion_kernel.cu:58-84): packed src [sum_len, head_num, size_per_head] ->
+ * dst [batch, head_num, max_seq_len, size_per_head], zeros where position >= seq_lens[b]. */
+EB_API int eb_transpose_pad(const void *src, void *dst, int batch, int max_seq_len, const int32_t *seq_lens, int head_num,
+                     int size_per_head, int dtype, void *stream);
+
+/* Replaces transpose_depad_wrapper (transpose_pad_fusion_wrapper.cpp:59-83, kernel
+ * transpose_pad_fusion_kernel.cu:8-35): src [batch, head_num, max_seq_len, size_per_head] ->
+ * dst [sum_seq, head_num, size_per_head]; rows of dst beyond sum(seq_lens) are zeroed. */
+EB_API int eb_transpose_depad(const void *src, void *dst, int batch, int sum_seq, int max_seq_len, const int32_t *seq_lens,
+                       int head_num, int size_per_head, int dtype, void *stream);
+
+/* ---- scale-mask-softmax ----------------------------------------------------------------- */
+
+/* Replaces scale_mask_softmax_wrapper (csrc/scale_mask_softmax_wrapper.cpp:25-44, kernel
+ * scale_mask_softmax_kernel.cu:12-42).  In place over scores [batch, head_num, seq_len,
+ * seq_len].  Reference behaviour = flags EB_SM_CAUSAL, scale 1.0f: rows i < real_seq_len[b]
+ * become softmax over keys j <= i with keys j > i set to 0, other rows are untouched.  The
+ * scores are multiplied by `scale` before the softmax.  No limit on seq_len (the reference
+ * stops at 1024).  dtype F32, F16 or BF16. */
+EB_API int eb_scale_mask_softmax(void *scores, const int32_t *real_seq_len, int batch, int seq_len, int head_num, int dtype,
+                          int flags, float scale, void *stream);
+
+/* ---- LayerNorm forward -------------------------------------------------------------------- */
+
+/* Replaces forward_affine (csrc/layer_norm_cuda.cpp:82-103, kernel
+ * layer_norm_cuda_kernel.cu:243-279) and the LayerNorm1D modules of the block
+ * (energonai/model/endecoder.py:28,39).  Rows n1, row length n2.
+ *   t   = x (+ residual) (+ bias[n2])            (optional operands may be NULL)
+ *   sum_out = t (in in_dtype), if sum_out != NULL
+ *   y   = gamma * (t - mean) * invvar + beta     (gamma/beta NULL: no affine)
+ *   mean[n1], invvar[n1] fp32, if non-NULL.
+ * Statistics in fp32 (two-pass over a register-resident row), biased variance. */
+EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x, const void *residual, const void *bias,
+                      void *sum_out, const void *gamma, const void *beta, int64_t n1, int n2, double eps, int in_dtype,
+                      int out_dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ENERGON_B200_H */
