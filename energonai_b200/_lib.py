@@ -17,7 +17,7 @@ ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2, 3
 SM_CAUSAL, SM_KEYLEN, SM_ALLROWS = 1, 2, 4
 
 _SCALARS = {"int": ctypes.c_int, "int32_t": ctypes.c_int32, "int64_t": ctypes.c_int64, "size_t": ctypes.c_size_t,
-            "float": ctypes.c_float, "double": ctypes.c_double, "unsigned": ctypes.c_uint, "uint64_t": ctypes.c_uint64}
+            "float": ctypes.c_float, "long long": ctypes.c_longlong, "double": ctypes.c_double, "unsigned": ctypes.c_uint, "uint64_t": ctypes.c_uint64}
 
 
 def parse_header(path=HEADER):
@@ -26,7 +26,7 @@ def parse_header(path=HEADER):
     decls = {}
     for m in re.finditer(r"EB_API\s+([\w\s\*]+?)\b(eb_\w+)\s*\(([^)]*)\)\s*;", text):
         ret, name, args = m.group(1).strip(), m.group(2), m.group(3).strip()
-        restype = ctypes.c_char_p if "*" in ret else _SCALARS[ret.split()[-1]]
+        restype = ctypes.c_char_p if "*" in ret else _SCALARS[ret]
         argtypes = []
         if args and args != "void":
             for a in args.split(","):
@@ -34,7 +34,8 @@ def parse_header(path=HEADER):
                 if "*" in a:
                     argtypes.append(ctypes.c_void_p)
                 else:
-                    argtypes.append(_SCALARS[a.replace("const", "").split()[0]])
+                    words = a.replace("const", "").split()[:-1]
+                    argtypes.append(_SCALARS[" ".join(words)])
         decls[name] = (restype, argtypes)
     return decls
 

@@ -1,0 +1,642 @@
+// Dense C = act(A · Wᵀ + bias) + residual on the 5th-generation tensor cores (tcgen05).
+//
+// Both operands are K-major 16-bit matrices (A [M,K], W [N,K]); accumulation is fp32 in
+// tensor memory.  One kernel template serves two orientations:
+//
+//   normal (M > 128): TMEM lanes = 128 rows of A, TMEM columns = BN rows of W.  Persistent
+//       CTAs walk output tiles in a grouped raster so that concurrently running CTAs share
+//       A and W panels in L2.
+//   swapped (M <= 128, decode): TMEM lanes = 128 rows of W, TMEM columns = the (padded) M
+//       rows of A.  The work is weight streaming, so it is cut stream-K style: the
+//       (tile, k-block) space is divided into equal contiguous ranges, one per CTA, every SM
+//       pulls the same number of weight bytes, and tiles shared by several CTAs are reduced
+//       through fp32 partials in a caller-provided workspace by whichever CTA arrives last
+//       (fixed summation order, so results are deterministic).
+//
+// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM allocation and
+// tcgen05.mma issue (one lane), warps 2-5 = epilogue (tcgen05.ld -> bias / activation /
+// residual -> global).  Shared-memory stages are handed over with mbarriers (full: TMA
+// transaction bytes; empty: tcgen05.commit), and two TMEM accumulators are ping-ponged so the
+// epilogue of one tile overlaps the main loop of the next.
+//
+// Every mbarrier wait is bounded by a wall-clock budget.  When it expires the CTA records
+// where it gave up in a device status word (eb_device_status), raises a CTA-wide abort flag so
+// the other roles leave their loops, lets in-flight copies land, frees its tensor memory and
+// returns; the context stays usable.
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace eb {
+namespace {
+
+constexpr int kLanes = 128;      // rows of the lane-side operand per tile (UMMA M)
+constexpr int kBlockK = 64;      // 64 x 16 bit = 128 bytes = one swizzle-128B row
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr int kGroup = 16;       // raster group height (lane-side tiles) in normal mode
+constexpr unsigned long long kWaitBudgetNs = 1000ull * 1000ull * 1000ull;
+
+__device__ int g_status[4];      // [0] code (0 = ok), [1] where, [2] block, [3] detail
+
+struct GemmParams {
+  int M, N, K;                   // logical problem: C[M,N] = A[M,K] W[N,K]^T
+  int lane_rows, col_rows;       // rows of the lane-side / column-side operand (swap: N, M)
+  int kblocks;                   // ceil(K / 64)
+  void *C;
+  long long ldc;
+  int c_rows_per_batch;          // 0: row m of C is at m*ldc; else (m / rpb)*c_batch_stride + (m % rpb)*ldc
+  long long c_batch_stride;
+  const void *bias;              // [N] or null
+  const void *residual;          // [M, N] rows ldr apart, or null
+  long long ldr;
+  int act;
+  int out_f32;                   // 1: C is fp32, else the input type
+  float *partial;                // stream-K partials (swap mode)
+  int *counters;                 // one per lane-side tile (swap mode), zero between calls
+  long long units_per_cta;       // stream-K: (tile, k-block) units per CTA
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting (this or another role ran out of time).
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int where) {
+  const unsigned long long t0 = globaltimer();
+  for (unsigned it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer() - t0 > kWaitBudgetNs) {
+        *abort_flag = 1;
+        if (atomicCAS(&g_status[0], 0, EB_ETIMEDOUT) == 0) {
+          g_status[1] = where;
+          g_status[2] = blockIdx.x;
+          g_status[3] = (int)parity;
+        }
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, where);
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups are 1024
+// bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: fp32 accumulate, A/B format (0 f16, 1 bf16), both K-major.
+__host__ __device__ constexpr uint32_t make_idesc(int n, int is_bf16) {
+  return (1u << 4) | ((uint32_t)is_bf16 << 7) | ((uint32_t)is_bf16 << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(kLanes >> 4) << 24);
+}
+
+// ---- work decomposition -----------------------------------------------------------------------
+struct Segment {
+  int lane_tile, col_tile;   // tile coordinates (lane-side, column-side)
+  int kb0, kb1;              // k-block range
+  bool partial;              // covers only part of K (swap mode)
+  int which;                 // 0: first segment of this CTA's range, 1: a later one
+};
+
+template <int BN, bool SWAP> struct Scheduler {
+  const GemmParams &p;
+  int lane_tiles, col_tiles;
+  long long pos, end;        // SWAP: unit range of this CTA;  normal: tile index / total tiles
+  bool first;
+  __device__ Scheduler(const GemmParams &pp) : p(pp) {
+    lane_tiles = (p.lane_rows + kLanes - 1) / kLanes;
+    col_tiles = (p.col_rows + BN - 1) / BN;
+    first = true;
+    if (SWAP) {
+      const long long total = (long long)lane_tiles * p.kblocks;   // col_tiles == 1 in swap mode
+      pos = (long long)blockIdx.x * p.units_per_cta;
+      end = pos + p.units_per_cta < total ? pos + p.units_per_cta : total;
+    } else {
+      pos = blockIdx.x;
+      end = (long long)lane_tiles * col_tiles;
+    }
+  }
+  __device__ bool next(Segment &s) {
+    if (pos >= end) return false;
+    if (SWAP) {
+      s.lane_tile = (int)(pos / p.kblocks);
+      s.col_tile = 0;
+      s.kb0 = (int)(pos % p.kblocks);
+      const long long left = end - pos;
+      s.kb1 = (long long)s.kb0 + left < p.kblocks ? (int)(s.kb0 + left) : p.kblocks;
+      s.partial = !(s.kb0 == 0 && s.kb1 == p.kblocks);
+      s.which = first ? 0 : 1;
+      pos += s.kb1 - s.kb0;
+    } else {
+      const int per_group = kGroup * col_tiles;
+      const int group = (int)(pos / per_group), in_group = (int)(pos % per_group);
+      const int first_lane = group * kGroup;
+      const int gsz = lane_tiles - first_lane < kGroup ? lane_tiles - first_lane : kGroup;
+      s.lane_tile = first_lane + in_group % gsz;
+      s.col_tile = in_group / gsz;
+      s.kb0 = 0;
+      s.kb1 = p.kblocks;
+      s.partial = false;
+      s.which = 0;
+      pos += gridDim.x;
+    }
+    first = false;
+    return true;
+  }
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == EB_ACT_RELU) return fmaxf(v, 0.f);
+  if (act == EB_ACT_GELU_TANH) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * v * (1.f + 0.044715f * v * v)));
+  if (act == EB_ACT_GELU_ERF) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  return v;
+}
+
+__device__ __forceinline__ long long c_row_offset(const GemmParams &p, int m) {
+  if (p.c_rows_per_batch <= 0) return (long long)m * p.ldc;
+  return (long long)(m / p.c_rows_per_batch) * p.c_batch_stride + (long long)(m % p.c_rows_per_batch) * p.ldc;
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------
+template <typename T, int BN, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__ CUtensorMap tm_col, const GemmParams p) {
+  constexpr uint32_t kLaneBytes = kLanes * 128, kColBytes = BN * 128, kStageBytes = kLaneBytes + kColBytes;
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  constexpr uint32_t kIdesc = make_idesc(BN, sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t *smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  const uint32_t tiles_addr = smem_u32(smem);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * kStageBytes);
+  const uint32_t full_bar = smem_u32(bars), empty_bar = full_bar + 8 * STAGES;
+  const uint32_t tfull_bar = empty_bar + 8 * STAGES, tempty_bar = tfull_bar + 16, epi_bar = tempty_bar + 16;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile int *last_flag = reinterpret_cast<volatile int *>(tmem_slot + 2);   // two entries, alternating
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(empty_bar + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar + 8 * a, 1);
+      mbar_init(tempty_bar + 8 * a, 4);   // one arrival per epilogue warp
+    }
+    mbar_init(epi_bar, 128);               // rendezvous of the four epilogue warps
+    *abort_flag = 0;
+    last_flag[0] = last_flag[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_lane) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_col) : "memory");
+  }
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      Scheduler<BN, SWAP> sched(p);
+      Segment s;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      while (ok && sched.next(s)) {
+        for (int kb = s.kb0; kb < s.kb1; ++kb) {
+          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, 1)) { ok = false; break; }
+          const uint32_t fb = full_bar + 8 * stage;
+          mbar_expect_tx(fb, kStageBytes);
+          const uint32_t dst = tiles_addr + stage * kStageBytes;
+          tma_load_2d(dst, &tm_lane, fb, kb * kBlockK, s.lane_tile * kLanes);
+          tma_load_2d(dst + kLaneBytes, &tm_col, fb, kb * kBlockK, s.col_tile * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      Scheduler<BN, SWAP> sched(p);
+      Segment s;
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      while (ok && sched.next(s)) {
+        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, 2)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = s.kb0; kb < s.kb1; ++kb) {
+          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t a_addr = tiles_addr + stage * kStageBytes;
+          const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + kLaneBytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // advancing 16 elements along K inside the swizzle atom = +32 bytes = +2 in the address field
+            tcgen05_mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (kb > s.kb0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(empty_bar + 8 * stage);   // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tcgen05_commit(tfull_bar + 8 * acc);        // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;                   // TMEM lane quarter this warp may access
+    const int lrow = quarter * 32 + lane;           // lane-side row inside the tile
+    const T *bias = reinterpret_cast<const T *>(p.bias);
+    const T *res = reinterpret_cast<const T *>(p.residual);
+    Scheduler<BN, SWAP> sched(p);
+    Segment s;
+    int acc = 0, flag_slot = 0;
+    uint32_t acc_phase = 0, epi_phase = 0;
+    bool alive = true;
+    // Rendezvous of the 128 epilogue threads with a bounded wait (a plain bar.sync could not
+    // be abandoned if one warp had already left on an abort).
+    auto epi_sync = [&]() {
+      mbar_arrive(epi_bar);
+      const bool ok = mbar_wait(epi_bar, epi_phase, abort_flag, 5);
+      epi_phase ^= 1u;
+      return ok;
+    };
+    while (alive && sched.next(s)) {
+      if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4)) break;
+      tcgen05_fence_after();
+      const uint32_t t_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+
+      if (!SWAP) {
+        const int m = s.lane_tile * kLanes + lrow;
+        const bool m_ok = m < p.M;
+        const long long c_off = m_ok ? c_row_offset(p, m) : 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 16; ++c) {
+          const int n0 = s.col_tile * BN + c * 16;
+          if (n0 >= p.N) break;                     // warp-uniform
+          float v[16];
+          tmem_ld16(t_base + c * 16, v);
+          if (m_ok) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {           // two groups of 8 columns (N is a multiple of 8)
+              const int n = n0 + h * 8;
+              if (n < p.N) {
+                float *vv = v + h * 8;
+                if (bias) {
+                  Vec16<T> b;
+                  b.load(bias + n);
+                  float bf[8];
+                  b.unpack(bf);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) vv[j] += bf[j];
+                }
+                if (p.act != EB_ACT_NONE) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) vv[j] = apply_act(vv[j], p.act);
+                }
+                if (res) {
+                  Vec16<T> r;
+                  r.load(res + (long long)m * p.ldr + n);
+                  float rf[8];
+                  r.unpack(rf);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) vv[j] += rf[j];
+                }
+                if (p.out_f32) {
+                  float4 *o = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.C) + c_off + n);
+                  o[0] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+                  o[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+                } else {
+                  Vec16<T> o;
+                  float tmp[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) tmp[j] = vv[j];
+                  o.pack(tmp);
+                  o.store(reinterpret_cast<T *>(p.C) + c_off + n);
+                }
+              }
+            }
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+      } else {
+        // swapped: this thread owns weight row n, TMEM columns are the batch rows m
+        const int n = s.lane_tile * kLanes + lrow;
+        const bool n_ok = n < p.N;
+        float v[BN];
+#pragma unroll
+        for (int c = 0; c < BN / 16; ++c) tmem_ld16(t_base + c * 16, v + c * 16);
+        // the accumulator is in registers: release it before any global traffic
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+
+        bool do_epilogue = true;
+        if (s.partial) {
+          float *mine = p.partial + ((size_t)(blockIdx.x * 2 + s.which) * BN) * kLanes;
+#pragma unroll
+          for (int m = 0; m < BN; ++m)
+            if (m < p.M) mine[(size_t)m * kLanes + lrow] = v[m];
+          __threadfence();
+          if (!epi_sync()) { alive = false; continue; }
+          // CTAs whose unit range intersects this tile
+          const long long t0 = (long long)s.lane_tile * p.kblocks;
+          const int first_cta = (int)(t0 / p.units_per_cta);
+          const int last_cta = (int)((t0 + p.kblocks - 1) / p.units_per_cta);
+          if (threadIdx.x == 64) {
+            const int arrived = atomicAdd(p.counters + s.lane_tile, 1);
+            const int is_last = arrived == last_cta - first_cta;
+            if (is_last) p.counters[s.lane_tile] = 0;      // ready for the next call
+            last_flag[flag_slot] = is_last;
+          }
+          if (!epi_sync()) { alive = false; continue; }
+          do_epilogue = last_flag[flag_slot] != 0;         // the other slot is written next time
+          flag_slot ^= 1;
+          if (do_epilogue) {
+            __threadfence();
+#pragma unroll
+            for (int m = 0; m < BN; ++m) v[m] = 0.f;
+            for (int cta = first_cta; cta <= last_cta; ++cta) {
+              // a CTA's piece of this tile is its first segment iff its range starts inside the tile
+              const int which = ((long long)cta * p.units_per_cta) / p.kblocks == s.lane_tile ? 0 : 1;
+              const float *theirs = p.partial + ((size_t)(cta * 2 + which) * BN) * kLanes;
+#pragma unroll
+              for (int m = 0; m < BN; ++m)
+                if (m < p.M) v[m] += __ldcg(theirs + (size_t)m * kLanes + lrow);
+            }
+          }
+        }
+        if (do_epilogue && n_ok) {
+          const float b = bias ? to_f32<T>(bias[n]) : 0.f;
+#pragma unroll
+          for (int m = 0; m < BN; ++m) {
+            if (m < p.M) {
+              float x = apply_act(v[m] + b, p.act);
+              if (res) x += to_f32<T>(res[(long long)m * p.ldr + n]);
+              const long long off = c_row_offset(p, m) + n;
+              if (p.out_f32) reinterpret_cast<float *>(p.C)[off] = x;
+              else reinterpret_cast<T *>(p.C)[off] = from_f32<T>(x);
+            }
+          }
+        }
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // bounded grace period for copies that may still be in flight to this CTA's shared memory
+    const unsigned long long t0 = globaltimer();
+    while (globaltimer() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D map over a row-major [rows, K] 16-bit matrix (row stride ld elements), box 64 x box_rows,
+// 128-byte swizzle, out-of-bounds elements read as zero.
+int make_map(CUtensorMap *map, const void *base, int dtype, long long rows, long long K, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(EB_ECUDA, "gemm: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dtype == EB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(EB_ECUDA, "gemm: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return EB_OK;
+}
+
+template <int BN, int STAGES> constexpr size_t smem_bytes() {
+  return (size_t)STAGES * (kLanes * 128 + BN * 128) + (2 * STAGES + 5) * 8 + 16 + 1024;
+}
+
+template <typename T, int BN, int STAGES, bool SWAP>
+int launch(const CUtensorMap &tl, const CUtensorMap &tc, const GemmParams &p, int grid, cudaStream_t st) {
+  auto kern = gemm_kernel<T, BN, STAGES, SWAP>;
+  constexpr size_t smem = smem_bytes<BN, STAGES>();
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(EB_ECUDA, "gemm: cannot reserve %zu bytes of shared memory", smem);
+    }
+    configured[dev] = true;
+  }
+  kern<<<grid, kThreads, smem, st>>>(tl, tc, p);
+  return check_launch("gemm");
+}
+
+inline int swap_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+
+// Stream-K split of the swapped orientation: grid and (tile, k-block) units per CTA.
+inline void swap_split(int N, int K, int *grid, long long *units) {
+  const long long tiles = (N + kLanes - 1) / kLanes, kblocks = (K + kBlockK - 1) / kBlockK;
+  const long long total = tiles * kblocks;
+  long long g = sm_count();
+  if (g > total / 4) g = total / 4 > 0 ? total / 4 : 1;   // at least 4 k-blocks per CTA
+  *units = (total + g - 1) / g;
+  *grid = (int)((total + *units - 1) / *units);
+}
+
+}  // namespace
+}  // namespace eb
+
+using namespace eb;
+
+extern "C" size_t eb_gemm_workspace_bytes(int M, int N, int K) {
+  if (M > kLanes || M <= 0 || N <= 0 || K <= 0) return 0;
+  int grid;
+  long long units;
+  swap_split(N, K, &grid, &units);
+  const size_t tiles = (N + kLanes - 1) / kLanes;
+  return (size_t)grid * 2 * swap_bn(M) * kLanes * sizeof(float) + tiles * sizeof(int) + 256;
+}
+
+extern "C" int eb_device_status(int *out4, int clear) {
+  int host[4] = {0, 0, 0, 0};
+  if (cudaMemcpyFromSymbol(host, g_status, sizeof(host)) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(EB_ECUDA, "device_status: cannot read the status word");
+  }
+  if (out4)
+    for (int i = 0; i < 4; ++i) out4[i] = host[i];
+  if (clear && host[0] != 0) {
+    int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_status, zero, sizeof(zero));
+  }
+  return EB_OK;
+}
+
+extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
+                       const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
+                       int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride, void *workspace,
+                       size_t workspace_bytes, void *stream) {
+  EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "gemm: operands must be fp16 or bf16 (got dtype %d)", dtype);
+  EB_REQUIRE(out_dtype == dtype || out_dtype == EB_F32, "gemm: output must be the input type or fp32");
+  EB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative size");
+  EB_REQUIRE(act >= EB_ACT_NONE && act <= EB_ACT_GELU_ERF, "gemm: unknown activation %d", act);
+  if (M == 0 || N == 0) return EB_OK;
+  EB_REQUIRE(A && W && C, "gemm: null operand");
+  EB_REQUIRE(K >= 8 && K % 8 == 0 && N % 8 == 0, "gemm: K and N must be positive multiples of 8 (K=%d N=%d)", K, N);
+  EB_REQUIRE(lda >= K && ldw >= K && lda % 8 == 0 && ldw % 8 == 0, "gemm: lda/ldw must be multiples of 8 and >= K");
+  EB_REQUIRE(ldc >= N && ldc % 8 == 0 && (!residual || (ldr >= N && ldr % 8 == 0)), "gemm: ldc/ldr must be multiples of 8 and >= N");
+  EB_REQUIRE(c_rows_per_batch >= 0 && (c_rows_per_batch == 0 || c_batch_stride % 8 == 0), "gemm: bad batch mapping of C");
+  EB_REQUIRE(aligned16(A) && aligned16(W) && aligned16(C) && aligned16(bias) && aligned16(residual),
+             "gemm: pointers must be 16-byte aligned");
+  cudaStream_t st = as_stream(stream);
+
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.kblocks = (K + kBlockK - 1) / kBlockK;
+  p.C = C; p.ldc = ldc; p.c_rows_per_batch = c_rows_per_batch; p.c_batch_stride = c_batch_stride;
+  p.bias = bias; p.residual = residual; p.ldr = ldr; p.act = act; p.out_f32 = out_dtype == EB_F32 && dtype != EB_F32;
+
+  CUtensorMap tl, tc;
+  int rc;
+  if (M <= kLanes) {
+    // swapped orientation: lanes = rows of W, columns = rows of A
+    const int bn = swap_bn(M);
+    int grid;
+    swap_split(N, K, &grid, &p.units_per_cta);
+    const size_t tiles = (N + kLanes - 1) / kLanes;
+    const size_t partial_bytes = (size_t)grid * 2 * bn * kLanes * sizeof(float);
+    const size_t need = partial_bytes + tiles * sizeof(int);
+    EB_REQUIRE(workspace && workspace_bytes >= need && aligned16(workspace),
+               "gemm: M=%d needs a zero-initialised workspace of %zu bytes (eb_gemm_workspace_bytes)", M, need);
+    p.partial = reinterpret_cast<float *>(workspace);
+    p.counters = reinterpret_cast<int *>(reinterpret_cast<char *>(workspace) + partial_bytes);
+    p.lane_rows = N; p.col_rows = M;
+    if ((rc = make_map(&tl, W, dtype, N, K, ldw, kLanes))) return rc;
+    if ((rc = make_map(&tc, A, dtype, M, K, lda, bn))) return rc;
+#define EB_SWAP(BN, ST)                                                                            \
+  (dtype == EB_F16 ? launch<__half, BN, ST, true>(tl, tc, p, grid, st)                             \
+                   : launch<__nv_bfloat16, BN, ST, true>(tl, tc, p, grid, st))
+    if (bn == 16) return EB_SWAP(16, 10);
+    if (bn == 32) return EB_SWAP(32, 10);
+    if (bn == 64) return EB_SWAP(64, 8);
+    return EB_SWAP(128, 6);
+#undef EB_SWAP
+  }
+  p.lane_rows = M; p.col_rows = N;
+  const long long lane_tiles = (M + kLanes - 1) / kLanes;
+  const bool wide = lane_tiles * ((N + 255) / 256) >= sm_count();   // enough 128x256 tiles to fill the machine
+  const int bn = wide ? 256 : 128;
+  const long long tiles = lane_tiles * ((N + bn - 1) / bn);
+  const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  if ((rc = make_map(&tl, A, dtype, M, K, lda, kLanes))) return rc;
+  if ((rc = make_map(&tc, W, dtype, N, K, ldw, bn))) return rc;
+  if (bn == 256)
+    return dtype == EB_F16 ? launch<__half, 256, 4, false>(tl, tc, p, grid, st)
+                           : launch<__nv_bfloat16, 256, 4, false>(tl, tc, p, grid, st);
+  return dtype == EB_F16 ? launch<__half, 128, 6, false>(tl, tc, p, grid, st)
+                         : launch<__nv_bfloat16, 128, 6, false>(tl, tc, p, grid, st);
+}

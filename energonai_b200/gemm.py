@@ -1,0 +1,61 @@
+"""Python entry to the tcgen05 GEMM (eb_gemm): C = act(A @ W.T + bias) + residual."""
+import torch
+
+from ._lib import lib, check, dtype_code, ptr, stream_ptr, require_cuda, ACT_NONE, ACT_RELU, ACT_GELU_TANH, ACT_GELU_ERF
+
+ACT_CODES = {None: ACT_NONE, "none": ACT_NONE, "relu": ACT_RELU, "gelu_tanh": ACT_GELU_TANH, "gelu": ACT_GELU_ERF}
+
+_workspaces = {}
+
+
+def workspace(device, nbytes):
+    """Per-device scratch for the small-M (decode) GEMM: zero-filled once, grown on demand.
+    One buffer per device is enough because calls on a device are issued on one stream."""
+    key = torch.device(device).index
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out_rows_per_batch=0,
+         out_batch_stride=0, out_ld=None):
+    """a [M,K] (row stride allowed), w [N,K]; returns out [M,N].
+
+    `out`, if given, receives the result; with out_rows_per_batch > 0 row m is written at
+    element (m // rpb) * out_batch_stride + (m % rpb) * out_ld of `out` (a view into a cache)."""
+    require_cuda(a, w, bias, residual, out)
+    if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1]:
+        raise RuntimeError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T do not match")
+    if a.dtype != w.dtype or a.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("gemm: fp16 or bf16 operands of one dtype required")
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if w.stride(1) != 1:
+        w = w.contiguous()
+    M, K = a.shape
+    N = w.shape[0]
+    out_dtype = out_dtype or a.dtype
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if out_ld is None:
+        out_ld = out.stride(0) if out.dim() == 2 else N
+    if residual is not None and (residual.stride(-1) != 1 or residual.dtype != a.dtype):
+        raise RuntimeError("gemm: residual must be row-major and of the operand dtype")
+    code = ACT_CODES[act] if not isinstance(act, int) else act
+    nbytes = lib().eb_gemm_workspace_bytes(M, N, K)
+    ws = workspace(a.device, nbytes) if nbytes else None
+    check(lib().eb_gemm(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out_ld, ptr(bias), ptr(residual),
+                        residual.stride(0) if residual is not None else 0, M, N, K, dtype_code(a.dtype),
+                        dtype_code(out_dtype), code, out_rows_per_batch, out_batch_stride, ptr(ws),
+                        ws.numel() if ws is not None else 0, stream_ptr()), "gemm")
+    return out
+
+
+def device_status(clear=True):
+    """(code, where, block, detail) of the current device's bounded-wait status word."""
+    import ctypes
+    buf = (ctypes.c_int * 4)()
+    check(lib().eb_device_status(ctypes.cast(buf, ctypes.c_void_p), 1 if clear else 0), "device_status")
+    return tuple(buf)

@@ -132,6 +132,36 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
                       void *sum_out, const void *gamma, const void *beta, int64_t n1, int n2, double eps, int in_dtype,
                       int out_dtype, void *stream);
 
+/* ---- dense layers (tcgen05 tensor-core GEMM) --------------------------------------------- */
+
+/* C = act(A . W^T + bias) + residual, fp32 accumulation in tensor memory.
+ * Replaces the F.linear inside the column-parallel and row-parallel layers the reference
+ * builds from colossalai (Linear1D_Col / Linear1D_Row, constructed at
+ * energonai/model/attention.py:29-37 and energonai/model/mlp.py:20-22) and mlp_gemm
+ * (energonai/kernel/cuda_native/csrc/linear_wrapper.cpp:82-111).
+ *   A [M,K] rows lda apart, W [N,K] rows ldw apart (both fp16 or both bf16, `dtype`);
+ *   C [M,N] in `out_dtype` (= dtype, or EB_F32); bias [N] (dtype) or NULL; residual [M,N]
+ *   rows ldr apart (dtype) or NULL; act one of EB_ACT_*.
+ *   Row m of C starts at element m*ldc, or, when c_rows_per_batch > 0, at
+ *   (m / c_rows_per_batch)*c_batch_stride + (m % c_rows_per_batch)*ldc  (this lets a
+ *   projection write straight into a [batch, max_len, width] cache at a position offset).
+ *   K, N, all leading dimensions and c_batch_stride must be multiples of 8, pointers 16-byte
+ *   aligned.
+ * For M <= 128 (decode) the kernel streams W once, split evenly over all SMs, and combines
+ * partial sums through `workspace`: at least eb_gemm_workspace_bytes(M,N,K) bytes, 16-byte
+ * aligned, zero-filled once before first use (the kernel leaves it reusable).  Calls that
+ * share a workspace must not overlap on the device.  workspace may be NULL for M > 128. */
+EB_API int eb_gemm(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc, const void *bias,
+            const void *residual, long long ldr, int M, int N, int K, int dtype, int out_dtype, int act,
+            int c_rows_per_batch, long long c_batch_stride, void *workspace, size_t workspace_bytes, void *stream);
+EB_API size_t eb_gemm_workspace_bytes(int M, int N, int K);
+
+/* Device-side waits are bounded; when one expires the kernel records it and returns.  This
+ * reads (synchronously) the status word of the current device: out4[0] = 0 or EB_ETIMEDOUT,
+ * out4[1] = which wait, out4[2] = block, out4[3] = detail.  clear != 0 resets it.  No
+ * counterpart in the reference, whose kernels have no waits. */
+EB_API int eb_device_status(int *out4, int clear);
+
 #ifdef __cplusplus
 }
 #endif
