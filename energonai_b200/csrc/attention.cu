@@ -1,0 +1,538 @@
+// Fused attention for the layer forward: scores, mask, softmax and the value product in one
+// pass, never materialising the [batch, heads, S, S] score tensor.
+//
+//   attention_prefill : all query rows of a prompt against all keys (flash-style: 64-query x
+//       64-key tiles, fp32 online softmax, tensor-core products).
+//   attention_decode  : one new query row per sequence against the cached keys/values.  The
+//       work is one pass over the cache (HBM-bound), so the key range of each (sequence,
+//       head) is split over several CTAs; partial (max, sum, output) triples go through a
+//       caller-provided fp32 scratch and the CTA that arrives last merges them.
+//
+// Masking follows energonai/model/attention.py:105-116: scores are scaled by head_dim^-0.5,
+// keys after the query are hidden when `causal`, and an optional additive per-key mask row
+// (0 / -10000 from the padding mask) is added before an fp32 softmax.  Hidden keys get weight
+// exactly 0 (the reference reaches the same through exp(-1e4) underflow).
+//
+// Q, K and V are addressed as [batch][row][head*D + d] with independent batch and row strides,
+// so they may be column slices of one fused projection / cache buffer.
+#include "common.cuh"
+
+namespace eb {
+namespace {
+
+constexpr int kBM = 64, kBN = 64, kThreads = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnParams {
+  const void *q, *k, *v;
+  void *o;
+  const void *mask;            // additive per-key mask [batch][kv_len] in the tensor dtype, or null
+  long long q_bs, q_rs, k_bs, k_rs, v_bs, v_rs, o_bs, o_rs, mask_bs;   // strides in elements
+  int B, H, Sq, Sk;            // Sk = kv length when kv_len_ptr is null
+  const int *kv_len_ptr;       // decode: device scalar with the current kv length (overrides Sk)
+  int causal;
+  float scale;
+  // decode split-KV
+  int nsplit;
+  float *scratch;              // [B*H][nsplit][D + 2]
+  int *counters;               // [B*H], zero between calls
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // src-size 0 zero-fills the destination
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+template <typename T> __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a [rows][D] 16-bit tile whose chunks are
+// XOR-swizzled with the row index (conflict-free ldmatrix and cp.async).
+template <int D> __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+  return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
+}
+
+// Load `kBN` rows starting at `row0` of a [*, D] slice (row stride rs elements) into a tile;
+// rows >= row_end are zero-filled.
+template <typename T, int D>
+__device__ __forceinline__ void load_tile(uint32_t tile, const T *base, long long rs, int row0, int row_end) {
+  constexpr int kChunks = D / 8;
+#pragma unroll
+  for (int i = threadIdx.x; i < kBN * kChunks; i += kThreads) {
+    const int r = i / kChunks, c = i % kChunks;
+    const bool ok = row0 + r < row_end;
+    const T *src = base + (long long)(ok ? row0 + r : row0) * rs + c * 8;
+    cp_async16(tile + tile_off<D>(r, c), src, ok);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// prefill
+// ------------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads)
+attention_prefill_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int kTileBytes = kBN * D * 2;
+  const uint32_t q_s = smem_u32(smem), k_s = q_s + kTileBytes, v_s = k_s + 2 * kTileBytes;
+  float *mask_s = reinterpret_cast<float *>(smem + 5 * kTileBytes);   // [2][kBN]
+
+  const int qt = gridDim.x - 1 - blockIdx.x;   // heavy (late) causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int Sq = p.Sq, Sk = p.Sk;
+  const int i0 = qt * kBM;
+  const int shift = Sk - Sq;                   // query i sees keys j <= i + shift under the causal mask
+
+  const T *qb = reinterpret_cast<const T *>(p.q) + b * p.q_bs + h * D;
+  const T *kb = reinterpret_cast<const T *>(p.k) + b * p.k_bs + h * D;
+  const T *vb = reinterpret_cast<const T *>(p.v) + b * p.v_bs + h * D;
+  const T *mb = p.mask ? reinterpret_cast<const T *>(p.mask) + b * p.mask_bs : nullptr;
+
+  int ntiles = (Sk + kBN - 1) / kBN;
+  if (p.causal) {
+    const int last_key = min(Sk - 1, i0 + kBM - 1 + shift);
+    ntiles = last_key < 0 ? 0 : last_key / kBN + 1;
+  }
+
+  load_tile<T, D>(q_s, qb, p.q_rs, i0, Sq);
+  auto load_kv = [&](int n, int buf) {
+    load_tile<T, D>(k_s + buf * kTileBytes, kb, p.k_rs, n * kBN, Sk);
+    load_tile<T, D>(v_s + buf * kTileBytes, vb, p.v_rs, n * kBN, Sk);
+    if (threadIdx.x < kBN) {
+      const int j = n * kBN + threadIdx.x;
+      mask_s[buf * kBN + threadIdx.x] = (mb && j < Sk) ? to_f32<T>(mb[j]) * kLog2e : 0.f;
+    }
+  };
+  if (ntiles > 0) load_kv(0, 0);
+  cp_async_commit();
+
+  uint32_t qf[D / 16][4];
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float sc = p.scale * kLog2e;
+  const int row_lo = i0 + warp * 16 + g;       // this thread's two query rows: row_lo, row_lo + 8
+
+  for (int n = 0; n < ntiles; ++n) {
+    const int buf = n & 1;
+    if (n + 1 < ntiles) load_kv(n + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (n == 0) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk)
+        ldmatrix_x4(qf[kk], q_s + tile_off<D>(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), kk * 2 + (lane >> 4)));
+    }
+    // S = Q K^T for 16 query rows x 64 keys
+    float s[kBN / 8][4];
+#pragma unroll
+    for (int i = 0; i < kBN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    const uint32_t kt = k_s + buf * kTileBytes, vt = v_s + buf * kTileBytes;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int nb = 0; nb < kBN / 16; ++nb) {
+        uint32_t kf[4];
+        ldmatrix_x4(kf, kt + tile_off<D>(nb * 16 + (lane & 7) + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
+        mma16816<T>(s[2 * nb], qf[kk], kf[0], kf[1]);
+        mma16816<T>(s[2 * nb + 1], qf[kk], kf[2], kf[3]);
+      }
+    }
+    // scale, mask
+    const int j0 = n * kBN;
+    const bool edge = (p.causal && j0 + kBN - 1 > i0 + warp * 16 + shift) || j0 + kBN > Sk;
+#pragma unroll
+    for (int i = 0; i < kBN / 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int jl = i * 8 + 2 * t + (e & 1);
+        float x = s[i][e] * sc + mask_s[buf * kBN + jl];
+        if (edge) {
+          const int j = j0 + jl, row = row_lo + (e >> 1) * 8;
+          if (j >= Sk || (p.causal && j > row + shift)) x = -INFINITY;
+        }
+        s[i][e] = x;
+      }
+    }
+    // online softmax for rows row_lo (e = 0,1) and row_lo + 8 (e = 2,3)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kBN / 8; ++i) mx = fmaxf(mx, fmaxf(s[i][2 * r], s[i][2 * r + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[r], mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float corr = exp2f(m_run[r] - m_use);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < kBN / 8; ++i) {
+        s[i][2 * r] = exp2f(s[i][2 * r] - m_use);
+        s[i][2 * r + 1] = exp2f(s[i][2 * r + 1] - m_use);
+        sum += s[i][2 * r] + s[i][2 * r + 1];
+      }
+      l_run[r] = l_run[r] * corr + sum;
+      m_run[r] = m_new;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) { o[i][2 * r] *= corr; o[i][2 * r + 1] *= corr; }
+    }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < kBN / 16; ++kk) {
+      uint32_t pf[4];
+      pf[0] = pack2<T>(s[2 * kk][0], s[2 * kk][1]);
+      pf[1] = pack2<T>(s[2 * kk][2], s[2 * kk][3]);
+      pf[2] = pack2<T>(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pf[3] = pack2<T>(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int db = 0; db < D / 16; ++db) {
+        uint32_t vf[4];
+        ldmatrix_x4_trans(vf, vt + tile_off<D>(kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), db * 2 + (lane >> 4)));
+        mma16816<T>(o[2 * db], pf, vf[0], vf[1]);
+        mma16816<T>(o[2 * db + 1], pf, vf[2], vf[3]);
+      }
+    }
+    __syncthreads();   // this buffer is refilled by the prefetch of the next iteration
+  }
+  cp_async_wait<0>();
+
+  // normalise, stage the 64 x D output tile through shared memory (Q's tile), store 16-byte rows
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const int row = warp * 16 + g + r * 8;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const uint32_t val = pack2<T>(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+      *reinterpret_cast<uint32_t *>(smem + tile_off<D>(row, i) + t * 4) = val;
+    }
+  }
+  __syncthreads();
+  T *ob = reinterpret_cast<T *>(p.o) + b * p.o_bs + h * D;
+  constexpr int kChunks = D / 8;
+  for (int i = threadIdx.x; i < kBM * kChunks; i += kThreads) {
+    const int r = i / kChunks, c = i % kChunks;
+    if (i0 + r < Sq)
+      *reinterpret_cast<uint4 *>(ob + (long long)(i0 + r) * p.o_rs + c * 8) =
+          *reinterpret_cast<const uint4 *>(smem + tile_off<D>(r, c));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// decode: one query row per (sequence, head); keys split over gridDim.x CTAs
+// ------------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads)
+attention_decode_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int kTileBytes = kBN * D * 2;
+  const uint32_t k_s = smem_u32(smem), v_s = k_s + 2 * kTileBytes;
+  float *mask_s = reinterpret_cast<float *>(smem + 4 * kTileBytes);            // [2][kBN]
+  float *red = mask_s + 2 * kBN;                                               // [4][D + 2] warp partials
+  __shared__ int s_last;
+
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int Sk = p.kv_len_ptr ? *p.kv_len_ptr : p.Sk;
+  const int tiles_total = (Sk + kBN - 1) / kBN;
+  const int tiles_per = (tiles_total + p.nsplit - 1) / p.nsplit;
+  const int tile0 = split * tiles_per, tile1 = min(tiles_total, tile0 + tiles_per);
+
+  const T *qrow = reinterpret_cast<const T *>(p.q) + b * p.q_bs + h * D;
+  const T *kb = reinterpret_cast<const T *>(p.k) + b * p.k_bs + h * D;
+  const T *vb = reinterpret_cast<const T *>(p.v) + b * p.v_bs + h * D;
+  const T *mb = p.mask ? reinterpret_cast<const T *>(p.mask) + b * p.mask_bs : nullptr;
+
+  auto load_kv = [&](int n, int buf) {
+    load_tile<T, D>(k_s + buf * kTileBytes, kb, p.k_rs, n * kBN, Sk);
+    load_tile<T, D>(v_s + buf * kTileBytes, vb, p.v_rs, n * kBN, Sk);
+    if (threadIdx.x < kBN) {
+      const int j = n * kBN + threadIdx.x;
+      mask_s[buf * kBN + threadIdx.x] = (mb && j < Sk) ? to_f32<T>(mb[j]) * kLog2e : 0.f;
+    }
+  };
+  if (tile0 < tile1) load_kv(tile0, 0);
+  cp_async_commit();
+
+  // A fragments of the single query row (row 0 of the 16-row MMA tile; the other rows are zero)
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    qf[kk][0] = qf[kk][1] = qf[kk][2] = qf[kk][3] = 0u;
+    if (g == 0) {
+      qf[kk][0] = *reinterpret_cast<const uint32_t *>(qrow + kk * 16 + 2 * t);
+      qf[kk][2] = *reinterpret_cast<const uint32_t *>(qrow + kk * 16 + 8 + 2 * t);
+    }
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  const float sc = p.scale * kLog2e;
+
+  for (int n = tile0; n < tile1; ++n) {
+    const int buf = (n - tile0) & 1;
+    if (n + 1 < tile1) load_kv(n + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t kt = k_s + buf * kTileBytes, vt = v_s + buf * kTileBytes;
+    // this warp's 16 keys of the tile: two 8-key n-tiles
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t kf[4];
+      ldmatrix_x4(kf, kt + tile_off<D>(warp * 16 + (lane & 7) + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
+      mma16816<T>(s[0], qf[kk], kf[0], kf[1]);
+      mma16816<T>(s[1], qf[kk], kf[2], kf[3]);
+    }
+    // row 0 lives in elements 0,1 of lanes with g == 0; other rows are ignored (kept finite)
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int jl = warp * 16 + i * 8 + 2 * t + e, j = n * kBN + jl;
+        float x = s[i][e] * sc + mask_s[buf * kBN + jl];
+        if (j >= Sk) x = -INFINITY;
+        s[i][e] = x;
+        mx = fmaxf(mx, x);
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    mx = __shfl_sync(0xffffffffu, mx, t);            // broadcast row 0's value (lanes 0..3 hold it)
+    const float m_new = fmaxf(m_run, mx);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+    const float corr = exp2f(m_run - m_use);
+    float pr[2][2];
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        pr[i][e] = g == 0 ? exp2f(s[i][e] - m_use) : 0.f;
+        sum += pr[i][e];
+      }
+    l_run = l_run * corr + sum;
+    m_run = m_new;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] *= corr; o[i][1] *= corr; }
+    uint32_t pf[4] = {pack2<T>(pr[0][0], pr[0][1]), 0u, pack2<T>(pr[1][0], pr[1][1]), 0u};
+#pragma unroll
+    for (int db = 0; db < D / 16; ++db) {
+      uint32_t vf[4];
+      ldmatrix_x4_trans(vf, vt + tile_off<D>(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), db * 2 + (lane >> 4)));
+      mma16816<T>(o[2 * db], pf, vf[0], vf[1]);
+      mma16816<T>(o[2 * db + 1], pf, vf[2], vf[3]);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // merge the four warps (each saw a quarter of every tile) -> one (m, l, o[D]) for this split
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  float *mine = red + warp * (D + 2);
+  if (g == 0) {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { mine[i * 8 + 2 * t] = o[i][0]; mine[i * 8 + 2 * t + 1] = o[i][1]; }
+    if (t == 0) { mine[D] = m_run; mine[D + 1] = l_run; }
+  }
+  __syncthreads();
+  float m_all = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) m_all = fmaxf(m_all, red[w * (D + 2) + D]);
+  const float m_ref = m_all == -INFINITY ? 0.f : m_all;
+  float l_all = 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) l_all += red[w * (D + 2) + D + 1] * exp2f(red[w * (D + 2) + D] - m_ref);
+  float acc = 0.f;   // thread d < D owns output dimension d
+  if (threadIdx.x < D) {
+#pragma unroll
+    for (int w = 0; w < 4; ++w) acc += red[w * (D + 2) + threadIdx.x] * exp2f(red[w * (D + 2) + D] - m_ref);
+  }
+  T *out = reinterpret_cast<T *>(p.o) + b * p.o_bs + h * D;
+  if (p.nsplit == 1) {
+    if (threadIdx.x < D) out[threadIdx.x] = from_f32<T>(l_all > 0.f ? acc / l_all : 0.f);
+    return;
+  }
+  const int bh = b * p.H + h;
+  float *slot = p.scratch + ((size_t)bh * p.nsplit + split) * (D + 2);
+  if (threadIdx.x < D) slot[threadIdx.x] = acc;
+  if (threadIdx.x == 0) { slot[D] = m_all; slot[D + 1] = l_all; }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int arrived = atomicAdd(p.counters + bh, 1);
+    s_last = arrived == p.nsplit - 1;
+    if (s_last) p.counters[bh] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float *all = p.scratch + (size_t)bh * p.nsplit * (D + 2);
+  float mm = -INFINITY;
+  for (int sidx = 0; sidx < p.nsplit; ++sidx) mm = fmaxf(mm, __ldcg(all + sidx * (D + 2) + D));
+  const float mref = mm == -INFINITY ? 0.f : mm;
+  float ll = 0.f, oo = 0.f;
+  for (int sidx = 0; sidx < p.nsplit; ++sidx) {
+    const float w = exp2f(__ldcg(all + sidx * (D + 2) + D) - mref);
+    ll += __ldcg(all + sidx * (D + 2) + D + 1) * w;
+    if (threadIdx.x < D) oo += __ldcg(all + sidx * (D + 2) + threadIdx.x) * w;
+  }
+  if (threadIdx.x < D) out[threadIdx.x] = from_f32<T>(ll > 0.f ? oo / ll : 0.f);
+}
+
+template <typename T, int D> int launch_prefill(const AttnParams &p, cudaStream_t st) {
+  constexpr size_t smem = 5 * (size_t)kBN * D * 2 + 2 * kBN * sizeof(float);
+  auto kern = attention_prefill_kernel<T, D>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(EB_ECUDA, "attention_prefill: cannot reserve %zu bytes of shared memory", smem);
+    }
+    configured[dev] = true;
+  }
+  dim3 grid((p.Sq + kBM - 1) / kBM, p.H, p.B);
+  kern<<<grid, kThreads, smem, st>>>(p);
+  return check_launch("attention_prefill");
+}
+
+template <typename T, int D> int launch_decode(const AttnParams &p, cudaStream_t st) {
+  constexpr size_t smem = 4 * (size_t)kBN * D * 2 + 2 * kBN * sizeof(float) + 4 * (D + 2) * sizeof(float);
+  auto kern = attention_decode_kernel<T, D>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(EB_ECUDA, "attention_decode: cannot reserve %zu bytes of shared memory", smem);
+    }
+    configured[dev] = true;
+  }
+  dim3 grid(p.nsplit, p.H, p.B);
+  kern<<<grid, kThreads, smem, st>>>(p);
+  return check_launch("attention_decode");
+}
+
+int check_common(const char *name, const AttnParams &p, int head_dim, int dtype) {
+  if (dtype != EB_F16 && dtype != EB_BF16) return fail(EB_EINVAL, "%s: fp16 or bf16 only (dtype %d)", name, dtype);
+  if (head_dim != 64 && head_dim != 128) return fail(EB_EUNSUPPORTED, "%s: head_dim %d not supported (64 or 128)", name, head_dim);
+  if (p.B < 0 || p.H < 0 || p.Sq < 0 || p.Sk < 0) return fail(EB_EINVAL, "%s: negative size", name);
+  if (p.H > 65535 || p.B > 65535) return fail(EB_ELIMIT, "%s: batch and heads are limited to 65535", name);
+  if (!p.q || !p.k || !p.v || !p.o) return fail(EB_EINVAL, "%s: null pointer", name);
+  if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.o))
+    return fail(EB_EINVAL, "%s: pointers must be 16-byte aligned", name);
+  const long long strides[] = {p.q_bs, p.q_rs, p.k_bs, p.k_rs, p.v_bs, p.v_rs, p.o_bs, p.o_rs};
+  for (long long s : strides)
+    if (s % 8 != 0) return fail(EB_EINVAL, "%s: strides must be multiples of 8 elements", name);
+  return EB_OK;
+}
+
+}  // namespace
+}  // namespace eb
+
+using namespace eb;
+
+extern "C" int eb_attention_prefill(const void *q, const void *k, const void *v, void *out, const void *mask,
+                                    long long q_batch_stride, long long q_row_stride, long long k_batch_stride,
+                                    long long k_row_stride, long long v_batch_stride, long long v_row_stride,
+                                    long long o_batch_stride, long long o_row_stride, long long mask_batch_stride,
+                                    int batch, int heads, int q_len, int kv_len, int head_dim, int causal, float scale,
+                                    int dtype, void *stream) {
+  AttnParams p{};
+  p.q = q; p.k = k; p.v = v; p.o = out; p.mask = mask;
+  p.q_bs = q_batch_stride; p.q_rs = q_row_stride; p.k_bs = k_batch_stride; p.k_rs = k_row_stride;
+  p.v_bs = v_batch_stride; p.v_rs = v_row_stride; p.o_bs = o_batch_stride; p.o_rs = o_row_stride;
+  p.mask_bs = mask_batch_stride;
+  p.B = batch; p.H = heads; p.Sq = q_len; p.Sk = kv_len; p.causal = causal; p.scale = scale; p.nsplit = 1;
+  if (batch == 0 || heads == 0 || q_len == 0) return EB_OK;
+  int rc = check_common("attention_prefill", p, head_dim, dtype);
+  if (rc) return rc;
+  EB_REQUIRE(kv_len >= q_len || !causal, "attention_prefill: causal attention needs kv_len >= q_len");
+  EB_REQUIRE(kv_len > 0, "attention_prefill: kv_len must be positive");
+  cudaStream_t st = as_stream(stream);
+  if (dtype == EB_F16) return head_dim == 64 ? launch_prefill<__half, 64>(p, st) : launch_prefill<__half, 128>(p, st);
+  return head_dim == 64 ? launch_prefill<__nv_bfloat16, 64>(p, st) : launch_prefill<__nv_bfloat16, 128>(p, st);
+}
+
+extern "C" size_t eb_attention_decode_scratch_bytes(int batch, int heads, int head_dim, int nsplit) {
+  if (batch <= 0 || heads <= 0 || nsplit <= 1) return 0;
+  return 64 * 1024 + (size_t)batch * heads * nsplit * (head_dim + 2) * sizeof(float);
+}
+
+extern "C" int eb_attention_decode(const void *q, const void *k, const void *v, void *out, const void *mask,
+                                   long long q_batch_stride, long long k_batch_stride, long long k_row_stride,
+                                   long long v_batch_stride, long long v_row_stride, long long o_batch_stride,
+                                   long long mask_batch_stride, int batch, int heads, int kv_len,
+                                   const int32_t *kv_len_device, int head_dim, float scale, int dtype, int nsplit,
+                                   void *scratch, size_t scratch_bytes, void *stream) {
+  AttnParams p{};
+  p.q = q; p.k = k; p.v = v; p.o = out; p.mask = mask;
+  p.q_bs = q_batch_stride; p.q_rs = 0; p.k_bs = k_batch_stride; p.k_rs = k_row_stride;
+  p.v_bs = v_batch_stride; p.v_rs = v_row_stride; p.o_bs = o_batch_stride; p.o_rs = 0;
+  p.mask_bs = mask_batch_stride;
+  p.B = batch; p.H = heads; p.Sq = 1; p.Sk = kv_len; p.kv_len_ptr = kv_len_device; p.causal = 0; p.scale = scale;
+  p.nsplit = nsplit;
+  if (batch == 0 || heads == 0) return EB_OK;
+  int rc = check_common("attention_decode", p, head_dim, dtype);
+  if (rc) return rc;
+  EB_REQUIRE(nsplit >= 1 && nsplit <= 1024, "attention_decode: nsplit must be in [1, 1024]");
+  EB_REQUIRE(kv_len > 0 || kv_len_device, "attention_decode: kv_len must be positive");
+  if (nsplit > 1) {
+    const size_t need = eb_attention_decode_scratch_bytes(batch, heads, head_dim, nsplit);
+    EB_REQUIRE((size_t)batch * heads * sizeof(int) <= 64 * 1024, "attention_decode: batch*heads exceeds the counter capacity (16384)");
+    EB_REQUIRE(scratch && scratch_bytes >= need && aligned16(scratch),
+               "attention_decode: nsplit=%d needs a scratch of %zu bytes, zero-filled once", nsplit, need);
+    p.counters = reinterpret_cast<int *>(scratch);
+    p.scratch = reinterpret_cast<float *>(reinterpret_cast<char *>(scratch) + 64 * 1024);
+  }
+  cudaStream_t st = as_stream(stream);
+  if (dtype == EB_F16) return head_dim == 64 ? launch_decode<__half, 64>(p, st) : launch_decode<__half, 128>(p, st);
+  return head_dim == 64 ? launch_decode<__nv_bfloat16, 64>(p, st) : launch_decode<__nv_bfloat16, 128>(p, st);
+}

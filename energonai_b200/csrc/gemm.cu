@@ -38,6 +38,7 @@ constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
 constexpr int kGroup = 16;       // raster group height (lane-side tiles) in normal mode
 constexpr unsigned long long kWaitBudgetNs = 1000ull * 1000ull * 1000ull;
+constexpr size_t kCounterBytes = 64 * 1024;   // workspace head: one int per lane-side tile, zero between calls
 
 __device__ int g_status[4];      // [0] code (0 = ok), [1] where, [2] block, [3] detail
 
@@ -557,8 +558,7 @@ extern "C" size_t eb_gemm_workspace_bytes(int M, int N, int K) {
   int grid;
   long long units;
   swap_split(N, K, &grid, &units);
-  const size_t tiles = (N + kLanes - 1) / kLanes;
-  return (size_t)grid * 2 * swap_bn(M) * kLanes * sizeof(float) + tiles * sizeof(int) + 256;
+  return kCounterBytes + (size_t)grid * 2 * swap_bn(M) * kLanes * sizeof(float);
 }
 
 extern "C" int eb_device_status(int *out4, int clear) {
@@ -608,12 +608,14 @@ extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ld
     int grid;
     swap_split(N, K, &grid, &p.units_per_cta);
     const size_t tiles = (N + kLanes - 1) / kLanes;
-    const size_t partial_bytes = (size_t)grid * 2 * bn * kLanes * sizeof(float);
-    const size_t need = partial_bytes + tiles * sizeof(int);
+    EB_REQUIRE(tiles * sizeof(int) <= kCounterBytes, "gemm: N=%d exceeds the decode path's tile-counter capacity", N);
+    // The counters sit at a fixed place (the head of the workspace) so that calls of any
+    // shape find them zero; the partials behind them need no initialisation.
+    const size_t need = kCounterBytes + (size_t)grid * 2 * bn * kLanes * sizeof(float);
     EB_REQUIRE(workspace && workspace_bytes >= need && aligned16(workspace),
-               "gemm: M=%d needs a zero-initialised workspace of %zu bytes (eb_gemm_workspace_bytes)", M, need);
-    p.partial = reinterpret_cast<float *>(workspace);
-    p.counters = reinterpret_cast<int *>(reinterpret_cast<char *>(workspace) + partial_bytes);
+               "gemm: M=%d needs a workspace of %zu bytes, zero-filled once (eb_gemm_workspace_bytes)", M, need);
+    p.counters = reinterpret_cast<int *>(workspace);
+    p.partial = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + kCounterBytes);
     p.lane_rows = N; p.col_rows = M;
     if ((rc = make_map(&tl, W, dtype, N, K, ldw, kLanes))) return rc;
     if ((rc = make_map(&tc, A, dtype, M, K, lda, bn))) return rc;

@@ -156,6 +156,40 @@ EB_API int eb_gemm(const void *A, long long lda, const void *W, long long ldw, v
             int c_rows_per_batch, long long c_batch_stride, void *workspace, size_t workspace_bytes, void *stream);
 EB_API size_t eb_gemm_workspace_bytes(int M, int N, int K);
 
+/* ---- fused attention ----------------------------------------------------------------------- */
+
+/* Replaces the score / mask / softmax / value products of MultiHeadAttention1D.forward
+ * (energonai/model/attention.py:105-124) for a whole prompt, without materialising the
+ * [batch, heads, q_len, kv_len] score tensor:
+ *   out[b,i,h,:] = softmax_j( scale * q[b,i,h,:].k[b,j,h,:] + mask[b,j] ; causal ) . v[b,j,h,:]
+ * q, k, v, out are addressed as base + b*batch_stride + row*row_stride + h*head_dim + d
+ * (elements), so they may be column slices of one fused projection buffer.  mask is an
+ * additive per-key row [batch][kv_len] in the tensor dtype (the reference's 0 / -10000
+ * padding mask) or NULL.  causal != 0 hides keys j > i + (kv_len - q_len).  head_dim 64 or
+ * 128, dtype fp16 or bf16, strides multiples of 8.  Softmax statistics are fp32. */
+EB_API int eb_attention_prefill(const void *q, const void *k, const void *v, void *out, const void *mask,
+                         long long q_batch_stride, long long q_row_stride, long long k_batch_stride,
+                         long long k_row_stride, long long v_batch_stride, long long v_row_stride,
+                         long long o_batch_stride, long long o_row_stride, long long mask_batch_stride, int batch,
+                         int heads, int q_len, int kv_len, int head_dim, int causal, float scale, int dtype,
+                         void *stream);
+
+/* The same product for one new query row per sequence against the cached keys/values (the
+ * generation step; replaces the torch.cat past_cache reads of attention.py:86-98 followed by
+ * attention.py:105-124).  q[b] is one row (base + b*q_batch_stride + h*head_dim); all kv_len
+ * cached keys are visible.  kv_len_device, if non-NULL, is a device int32 that overrides
+ * kv_len at run time (so a captured launch can be replayed while the cache grows).  The key
+ * range is split over `nsplit` CTAs per (sequence, head); for nsplit > 1 `scratch` must hold
+ * eb_attention_decode_scratch_bytes(...) bytes, 16-byte aligned, zero-filled once before
+ * first use.  Calls sharing a scratch must not overlap on the device. */
+EB_API int eb_attention_decode(const void *q, const void *k, const void *v, void *out, const void *mask,
+                        long long q_batch_stride, long long k_batch_stride, long long k_row_stride,
+                        long long v_batch_stride, long long v_row_stride, long long o_batch_stride,
+                        long long mask_batch_stride, int batch, int heads, int kv_len, const int32_t *kv_len_device,
+                        int head_dim, float scale, int dtype, int nsplit, void *scratch, size_t scratch_bytes,
+                        void *stream);
+EB_API size_t eb_attention_decode_scratch_bytes(int batch, int heads, int head_dim, int nsplit);
+
 /* Device-side waits are bounded; when one expires the kernel records it and returns.  This
  * reads (synchronously) the status word of the current device: out4[0] = 0 or EB_ETIMEDOUT,
  * out4[1] = which wait, out4[2] = block, out4[3] = detail.  clear != 0 resets it.  No
