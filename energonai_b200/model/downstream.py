@@ -1,0 +1,36 @@
+"""LMHead1D with the reference's interface (energonai/model/downstream.py:5-26): a bias-free
+(by default) projection to the vocabulary on the tcgen05 GEMM, logits in fp32."""
+import torch
+from torch import dtype, nn
+
+from ..gemm import gemm
+
+
+class _Classifier(nn.Module):
+    def __init__(self, in_features, num_classes, weight=None, bias=False, dtype=None):
+        super().__init__()
+        self.weight = weight if weight is not None else nn.Parameter(torch.empty(num_classes, in_features, dtype=dtype))
+        if weight is None:
+            nn.init.normal_(self.weight, std=0.02)
+        self.bias = nn.Parameter(torch.zeros(num_classes, dtype=dtype)) if bias else None
+
+    def forward(self, x):
+        y = gemm(x.reshape(-1, x.shape[-1]), self.weight, bias=self.bias, out_dtype=torch.float32)
+        return y.view(*x.shape[:-1], self.weight.shape[0])
+
+
+class LMHead1D(nn.Module):
+    def __init__(self, hidden_size: int, vocab_size: int, word_embedding_weight: nn.Parameter = None,
+                 bias: bool = False, dtype: dtype = None, vocab_parallel: bool = False) -> None:
+        super().__init__()
+        if vocab_parallel:
+            raise RuntimeError("vocab-parallel LM head is not implemented (replicated head only)")
+        self.vocab_parallel = vocab_parallel
+        self.dense = _Classifier(hidden_size, vocab_size, word_embedding_weight, bias=bias, dtype=dtype)
+
+    @property
+    def weight(self):
+        return self.dense.weight
+
+    def forward(self, x):
+        return self.dense(x)

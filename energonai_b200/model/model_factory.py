@@ -1,0 +1,216 @@
+"""PipelineModel and the model factories with the reference's interface
+(energonai/model/model_factory.py:43-354), single pipeline stage.
+
+The generation loop keeps the reference's contract (input_ids / attention_mask in, token ids
+extended to max_tokens out; sampling through the same logits warpers; greedy = top_k 1) but
+does the work once: the prompt is embedded and run through the blocks a single time, every
+later step embeds and runs only the new token against the key/value caches, and the final
+norm + LM head see only the last position (the reference re-embeds the whole sequence and
+runs the head on every position each step, model_factory.py:112-131, with the same result for
+the sampled token)."""
+from typing import Callable, Optional
+
+import torch
+from torch import dtype, nn
+
+from ..nn import LayerNorm1D
+from .downstream import LMHead1D
+from .embedding import Embedding1D
+from .endecoder import Block1D
+from .mlp import gelu_impl
+
+
+class PipelineModel(nn.Module):
+    def __init__(self,
+                 vocab_size: int = 50257,
+                 num_tokentypes: int = 0,
+                 max_seq_len: int = 512,
+                 hidden_size: int = 768,
+                 num_heads: int = 12,
+                 depth: int = 12,
+                 mlp_ratio: float = 4.0,
+                 layernorm_epsilon: float = 1e-5,
+                 activation: Callable = gelu_impl,
+                 padding_idx: int = 0,
+                 dtype: dtype = torch.float16,
+                 bias: bool = True,
+                 apply_post_layernorm: bool = False,
+                 first: bool = True,
+                 last: bool = True,
+                 fused_qkv: bool = True,
+                 checkpoint: str = None,
+                 model_name: str = None,
+                 is_decoder: bool = True,
+                 disable_past_cache=False,
+                 vocab_parallel: bool = False) -> None:
+        super().__init__()
+        self.hidden_size, self.first, self.last = hidden_size, first, last
+        self.max_seq_len, self.model_name = max_seq_len, model_name
+        self.disable_past_cache = disable_past_cache
+        self.eos_token_id = 50256          # the reference hard-codes this stop id (model_factory.py:133)
+        if first:
+            self.embed = Embedding1D(hidden_size=hidden_size, vocab_size=vocab_size, max_seq_len=max_seq_len,
+                                     num_tokentypes=num_tokentypes, padding_idx=padding_idx, dtype=dtype,
+                                     vocab_parallel=vocab_parallel)
+        self.blocks = nn.ModuleList()
+        for id_ in range(depth):
+            self.blocks.add_module(f'{id_}', Block1D(hidden_size=hidden_size, num_heads=num_heads, mlp_ratio=mlp_ratio,
+                                                     activation=activation, layernorm_epsilon=layernorm_epsilon,
+                                                     dtype=dtype, bias=bias, apply_post_layernorm=apply_post_layernorm,
+                                                     max_seq_len=max_seq_len, fused_qkv=fused_qkv, is_decoder=is_decoder,
+                                                     disable_past_cache=disable_past_cache))
+        if last:
+            self.norm = LayerNorm1D(normalized_shape=hidden_size, eps=layernorm_epsilon, dtype=dtype)
+            self.head = LMHead1D(hidden_size=hidden_size, vocab_size=vocab_size, bias=False, dtype=dtype,
+                                 vocab_parallel=vocab_parallel)
+
+    def reserve_cache(self, new_tokens):
+        """Size the key/value caches so `new_tokens` generation steps need no reallocation."""
+        for blk in self.blocks:
+            blk.attn.past_cache.reserve = max(1, int(new_tokens))
+
+    @torch.inference_mode()
+    def forward(self, hidden_states=None, input_ids=None, attention_mask=None, seq_lens=None,
+                max_tokens: Optional[int] = None, top_k: Optional[int] = None, top_p: Optional[float] = None,
+                temperature: Optional[float] = None, record=None):
+        batch_size, cur_len = input_ids.shape
+        tgt_len = cur_len + 1 if not max_tokens else max_tokens
+        if cur_len >= tgt_len:
+            return input_ids
+        if attention_mask is None:
+            attention_mask = torch.ones_like(input_ids)
+        dev = input_ids.device
+        model_dtype = self.norm.module.weight.dtype if self.last else self.blocks[0].norm1.module.weight.dtype
+        self.reserve_cache(tgt_len - cur_len)
+        # additive key mask for every position the sequence may reach: (1 - mask) * -10000, then 0
+        add_mask = torch.zeros((batch_size, tgt_len), dtype=model_dtype, device=dev)
+        add_mask[:, :cur_len] = (1.0 - attention_mask.view(batch_size, -1).to(model_dtype)) * -10000.0
+        out_ids = torch.empty((batch_size, tgt_len), dtype=input_ids.dtype, device=dev)
+        out_ids[:, :cur_len] = input_ids
+        greedy = top_k == 1 and (temperature is None or temperature > 0)
+        step_ids, past = input_ids, 0
+        first_cache = True
+        tok = None
+        for pos in range(cur_len, tgt_len):
+            hidden_states = self.embed(step_ids, past_key_values_length=past) if self.first else hidden_states
+            mask4 = add_mask[:, :pos].view(batch_size, 1, 1, pos)
+            if self.disable_past_cache and not first_cache:
+                hidden_states = self.embed(out_ids[:, :pos])
+            for block in self.blocks:
+                hidden_states = block(hidden_states=hidden_states, attention_mask=mask4, first_cache=first_cache)
+            if self.last:
+                last_hidden = self.norm(hidden_states[:, -1:, :].contiguous())
+                logits = self.head(last_hidden)[:, -1, :]
+                if record is not None:
+                    record.setdefault("logits", []).append(logits.clone())
+                    record.setdefault("hidden", []).append(last_hidden[:, -1, :].clone())
+                tok = logits.argmax(-1) if greedy else self.generate(out_ids[:, :pos], logits, top_k=top_k, top_p=top_p,
+                                                                     temperature=temperature)
+            if torch.all(tok == self.eos_token_id):
+                return out_ids[:, :pos] if max_tokens else tok
+            out_ids[:, pos] = tok
+            step_ids, past, first_cache = tok.view(-1, 1), pos, False
+        return out_ids if max_tokens else tok
+
+    def get_logits_processor(self, top_k=None, top_p=None, temperature=None):
+        from transformers.generation import (LogitsProcessorList, TemperatureLogitsWarper, TopKLogitsWarper,
+                                             TopPLogitsWarper)
+        processor_list = LogitsProcessorList()
+        if temperature is not None and temperature != 1.0:
+            processor_list.append(TemperatureLogitsWarper(temperature))
+        if top_k is not None and top_k != 0:
+            processor_list.append(TopKLogitsWarper(top_k))
+        if top_p is not None and top_p < 1.0:
+            processor_list.append(TopPLogitsWarper(top_p))
+        return processor_list
+
+    def generate(self, input_ids, logits, top_k=None, top_p=None, temperature=None):
+        """model_factory.py:153-159 on last-position logits [batch, vocab]."""
+        logits = self.get_logits_processor(top_k, top_p, temperature)(input_ids, logits)
+        probs = torch.softmax(logits, -1, dtype=torch.float)
+        return torch.multinomial(probs, num_samples=1).squeeze(1)
+
+
+def create_pipeline_model(depth: int = 48, layer_partitions=None, **model_kwargs):
+    """Single-stage version of model_factory.py:182-226 (pipeline parallelism is outside the
+    tensor-parallel layer path this package implements)."""
+    if layer_partitions is not None:
+        raise RuntimeError("pipeline partitioning is not supported; run with one pipeline stage")
+    model_kwargs = dict(model_kwargs)
+    for k in ("checkpoint",):
+        if model_kwargs.get(k):
+            raise RuntimeError("checkpoint loading is not implemented; load a state_dict with the reference's names")
+    model_kwargs.update(first=True, last=True, depth=depth)
+    model = PipelineModel(**model_kwargs)
+    return model.cuda() if torch.cuda.is_available() else model
+
+
+def _opt(hidden, depth, heads, **kwargs):
+    model_kwargs = dict(vocab_size=50272, hidden_size=hidden, depth=depth, max_seq_len=2050, num_heads=heads,
+                        activation=nn.functional.relu, is_decoder=True, fused_qkv=False, model_name="opt",
+                        disable_past_cache=False)
+    model_kwargs.update(kwargs)
+    return create_pipeline_model(**model_kwargs)
+
+
+def opt_125M(**kwargs):
+    return _opt(768, 12, 12, **kwargs)
+
+
+def opt_6B(**kwargs):
+    return _opt(4096, 32, 32, **kwargs)
+
+
+def opt_13B(**kwargs):
+    """OPT-13B shape (40 layers, hidden 5120, 40 heads); the reference has no factory of this
+    name, the shape follows its opt_* pattern (model_factory.py:281-339)."""
+    return _opt(5120, 40, 40, **kwargs)
+
+
+def opt_30B(**kwargs):
+    return _opt(7168, 48, 56, **kwargs)
+
+
+def opt_66B(**kwargs):
+    return _opt(9216, 64, 72, **kwargs)
+
+
+def opt_175B(**kwargs):
+    return _opt(12288, 96, 96, **dict(dict(fused_qkv=True, model_name="opt-175b"), **kwargs))
+
+
+def gpt2_small(**kwargs):
+    return create_pipeline_model(**dict(dict(hidden_size=768, depth=12, num_heads=12, is_decoder=True), **kwargs))
+
+
+def gpt2_large(**kwargs):
+    return create_pipeline_model(**dict(dict(hidden_size=1536, depth=36, num_heads=12, is_decoder=True), **kwargs))
+
+
+def gpt2_8B(**kwargs):
+    return create_pipeline_model(**dict(dict(hidden_size=3072, depth=72, num_heads=24, is_decoder=True), **kwargs))
+
+
+def gpt3(**kwargs):
+    return create_pipeline_model(**dict(dict(hidden_size=12288, depth=12, num_heads=96, is_decoder=True), **kwargs))
+
+
+def hf_gpt2(**kwargs):
+    return create_pipeline_model(**dict(dict(hidden_size=768, depth=12, max_seq_len=1024, num_heads=12, fused_qkv=False,
+                                             model_name="hf_gpt2", is_decoder=True), **kwargs))
+
+
+def bert_small(**kwargs):
+    return create_pipeline_model(**dict(dict(hidden_size=768, depth=12, num_heads=12, is_decoder=False), **kwargs))
+
+
+def bert_large(**kwargs):
+    return create_pipeline_model(**dict(dict(hidden_size=1024, depth=24, num_heads=16, is_decoder=False), **kwargs))
+
+
+def bert_8B(**kwargs):
+    return create_pipeline_model(**dict(dict(hidden_size=3072, depth=72, num_heads=24, is_decoder=False), **kwargs))
+
+
+def bert_175B(**kwargs):
+    return create_pipeline_model(**dict(dict(hidden_size=12288, depth=96, num_heads=96, is_decoder=False), **kwargs))

@@ -1,0 +1,76 @@
+"""The 1-D tensor-parallel building blocks the reference imports from colossalai
+(Linear1D_Col, Linear1D_Row, LayerNorm1D; used at energonai/model/attention.py:29-37,
+mlp.py:20-22, endecoder.py:28,39), on the tcgen05 GEMM and the fused LayerNorm kernel.
+
+Semantics (Megatron 1-D):
+  Linear1D_Col  y_r = x W_r^T + b_r,  W split on dim 0 (each rank owns out/t rows), no
+                communication unless gather_output.
+  Linear1D_Row  y = allreduce_r(x_r W_r^T) + b,  W split on dim 1 (each rank owns in/t
+                columns), bias added once after the reduction.
+  LayerNorm1D   replicated affine LayerNorm; the parameters live on a child called `module`,
+                which gives the reference's state_dict names (norm1.module.weight ...).
+"""
+import torch
+from torch import nn
+
+from .gemm import gemm
+from .kernel.cuda_native.layer_norm import layer_norm_forward
+from .tp import get_tp, divide
+
+
+def _flat(x):
+    return x.reshape(-1, x.shape[-1])
+
+
+class Linear1D_Col(nn.Module):
+    def __init__(self, in_features, out_features, bias=True, dtype=None, gather_output=False, device=None):
+        super().__init__()
+        tp = get_tp()
+        self.in_features, self.out_features, self.gather_output = in_features, out_features, gather_output
+        self.out_per_rank = divide(out_features, tp.world_size)
+        self.weight = nn.Parameter(torch.empty(self.out_per_rank, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(self.out_per_rank, dtype=dtype, device=device)) if bias else None
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, x, act=None):
+        y = gemm(_flat(x), self.weight, bias=self.bias, act=act).view(*x.shape[:-1], self.out_per_rank)
+        return get_tp().all_gather_last_dim(y) if self.gather_output else y
+
+
+class Linear1D_Row(nn.Module):
+    def __init__(self, in_features, out_features, bias=True, dtype=None, parallel_input=True, device=None):
+        super().__init__()
+        tp = get_tp()
+        self.in_features, self.out_features = in_features, out_features
+        self.in_per_rank = divide(in_features, tp.world_size)
+        self.weight = nn.Parameter(torch.empty(out_features, self.in_per_rank, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+        nn.init.normal_(self.weight, std=0.02)
+
+    def forward(self, x, residual=None):
+        """x is this rank's slice of the input features.  Bias (and an optional residual) enter
+        the sum exactly once: rank 0 adds them in its GEMM epilogue, then the partial products
+        are all-reduced."""
+        tp = get_tp()
+        lead = tp.rank == 0
+        res = _flat(residual) if (residual is not None and lead) else None
+        y = gemm(_flat(x), self.weight, bias=self.bias if lead else None, residual=res)
+        tp.all_reduce(y)
+        return y.view(*x.shape[:-1], self.out_features)
+
+
+class _LayerNormParams(nn.Module):
+    def __init__(self, n, dtype, device):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(n, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(n, dtype=dtype, device=device))
+
+
+class LayerNorm1D(nn.Module):
+    def __init__(self, normalized_shape, eps=1e-5, dtype=None, device=None):
+        super().__init__()
+        self.normalized_shape, self.eps = int(normalized_shape), eps
+        self.module = _LayerNormParams(self.normalized_shape, dtype, device)
+
+    def forward(self, x):
+        return layer_norm_forward(_flat(x), self.module.weight, self.module.bias, self.eps).view(x.shape)

@@ -1,0 +1,58 @@
+"""Tensor-parallel context: which rank of which group this process is, and the all-reduce the
+row-parallel layers use.
+
+The reference gets this from colossalai's global context (`gpc`, ParallelMode.PARALLEL_1D;
+set up by colossalai.launch at energonai/worker.py:27-28).  Here it is a small explicit object
+over torch.distributed: one process per GPU, NCCL over NVLink as the collective backend.
+With no context installed every layer behaves as tensor-parallel size 1.
+"""
+import torch
+import torch.distributed as dist
+
+
+class TPContext:
+    def __init__(self, group=None, rank=0, world_size=1):
+        self.group, self.rank, self.world_size = group, rank, world_size
+
+    def all_reduce(self, t):
+        """In-place SUM over the tensor-parallel group (no-op for one rank)."""
+        if self.world_size > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def all_gather_last_dim(self, t):
+        if self.world_size == 1:
+            return t
+        parts = [torch.empty_like(t) for _ in range(self.world_size)]
+        dist.all_gather(parts, t.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+
+_ctx = TPContext()
+
+
+def get_tp():
+    return _ctx
+
+
+def set_tp(ctx):
+    global _ctx
+    _ctx = ctx if ctx is not None else TPContext()
+    return _ctx
+
+
+def init_tp(tp_world_size=None, group=None):
+    """Installs a context over an initialised torch.distributed default group (or `group`)."""
+    if not dist.is_initialized():
+        return set_tp(TPContext())
+    group = group if group is not None else dist.group.WORLD
+    ws = dist.get_world_size(group)
+    if tp_world_size is not None and tp_world_size != ws:
+        raise RuntimeError(f"tensor-parallel size {tp_world_size} does not match the process group size {ws}")
+    return set_tp(TPContext(group, dist.get_rank(group), ws))
+
+
+def divide(numerator, denominator):
+    if numerator % denominator != 0:
+        raise ValueError(f"{numerator} is not divisible by {denominator}")
+    return numerator // denominator

@@ -26,8 +26,9 @@ BLOCK_CASES = {
     "preln_decoder_unfused": (False, False, True, "relu", "left"),
     "postln_encoder_fused": (True, True, False, "gelu", "right"),
 }
-BLOCK_DIMS = dict(hidden=64, heads=4, ffn=256, B=3, S=12, steps=2)
-TINY = dict(vocab=512, max_pos=64, hidden=64, heads=4, ffn=256, depth=2, B=4, S=16, new=8)
+# head dimension 64 (= hidden / heads), the smallest the fused attention kernels implement
+BLOCK_DIMS = dict(hidden=256, heads=4, ffn=1024, B=3, S=12, steps=2)
+TINY = dict(vocab=512, max_pos=64, hidden=128, heads=2, ffn=512, depth=2, B=4, S=16, new=8)
 CFG1 = dict(vocab=50272, max_pos=2050, hidden=768, heads=12, ffn=3072, depth=12, B=8, S=128, new=32)
 
 
