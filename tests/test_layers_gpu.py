@@ -20,10 +20,15 @@ mg = importlib.util.module_from_spec(spec)
 spec.loader.exec_module(mg)
 
 
-def assert_close(out, ref, what=""):
+def assert_close(out, ref, what="", row_relative=False):
+    """Elementwise |out - ref| <= 2e-2 + 1e-2*|ref|.  With row_relative (used for bf16 on the
+    large-activation fixture) the relative part is taken against the largest activation of the
+    row: bf16 keeps 8 mantissa bits, so one rounding of a residual-stream value near 4 is already
+    1.6e-2, and a block output has gone through seven such roundings."""
     out, ref = out.float().cpu(), ref.float().cpu()
     err = (out - ref).abs()
-    bound = 2e-2 + 1e-2 * ref.abs()
+    scale = ref.abs().amax(-1, keepdim=True) if row_relative else ref.abs()
+    bound = 2e-2 + 1e-2 * scale
     assert (err <= bound).all(), f"{what}: max err {err.max():.4g}, worst excess {(err - bound).max():.4g}"
 
 
@@ -50,6 +55,7 @@ def test_block_against_reference_fixture(name, dtype):
     blk, x, mask, side = build_block(name, dtype)
     B, S = d["B"], d["S"]
     valid = mask.bool()
+    rr = dtype == torch.bfloat16
     with torch.inference_mode():
         for step in range(d["steps"] + 1):
             cur = S + step
@@ -61,10 +67,10 @@ def test_block_against_reference_fixture(name, dtype):
                 assert out.shape == ref.shape
                 # left-padding query rows are unspecified; every other row is compared
                 rows = valid if side == "left" else torch.ones_like(valid)
-                assert_close(out.cpu()[rows], ref[rows], f"{name} prefill")
+                assert_close(out.cpu()[rows], ref[rows], f"{name} prefill", rr)
             else:
                 assert out.shape == (B, 1, d["hidden"])          # generation steps return the new position only
-                assert_close(out[:, -1], ref[:, -1], f"{name} step {step}")
+                assert_close(out[:, -1], ref[:, -1], f"{name} step {step}", rr)
 
 
 def test_block_decode_accepts_last_position_only():
