@@ -61,7 +61,12 @@ def last_error():
     return lib().eb_last_error().decode()
 
 
+launch_count = 0     # successful compute calls through the C ABI (each launches exactly one kernel)
+
+
 def check(rc, what=""):
+    global launch_count
+    launch_count += 1
     if rc != 0:
         raise RuntimeError(f"energon_b200 {what} failed ({rc}): {last_error()}")
 

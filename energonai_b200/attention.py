@@ -50,10 +50,16 @@ def pick_nsplit(batch, heads, kv_len, sm_count=148):
     return max(1, min(want, tiles, 64))
 
 
-def attention_decode(q, k, v, head_dim, kv_len, mask=None, scale=None, out=None, nsplit=None, kv_len_device=None):
+def attention_decode(q, k, v, head_dim, kv_len, mask=None, scale=None, out=None, nsplit=None, kv_len_device=None,
+                     q_in_cache=False):
     """q [B, H*D] (one row per sequence), k/v [B, >=kv_len, H*D] cache views, mask [B, >=kv_len].
+    With q_in_cache, q is a [B, capacity, H*D] view like k/v and the query is its row kv_len-1.
     Returns out [B, H*D]."""
     require_cuda(q, k, v, mask, out, kv_len_device)
+    q_rs = 0
+    if q_in_cache:
+        q_rs = q.stride(1)
+        q = q[:, 0]
     B, HD = q.shape
     H = HD // head_dim
     if q.stride(1) != 1:
@@ -68,7 +74,7 @@ def attention_decode(q, k, v, head_dim, kv_len, mask=None, scale=None, out=None,
     nbytes = lib().eb_attention_decode_scratch_bytes(B, H, head_dim, nsplit)
     scratch = _get_scratch(q.device, nbytes) if nbytes else None
     scale = head_dim ** -0.5 if scale is None else scale
-    check(lib().eb_attention_decode(ptr(q), ptr(k), ptr(v), ptr(out), ptr(mask), q.stride(0), ks[0], ks[1], vs[0], vs[1],
+    check(lib().eb_attention_decode(ptr(q), ptr(k), ptr(v), ptr(out), ptr(mask), q.stride(0), q_rs, ks[0], ks[1], vs[0], vs[1],
                                     out.stride(0), mask.stride(0) if mask is not None else 0, B, H, int(kv_len),
                                     ptr(kv_len_device), head_dim, float(scale), dtype_code(q.dtype), nsplit, ptr(scratch),
                                     scratch.numel() if scratch is not None else 0, stream_ptr()), "attention_decode")

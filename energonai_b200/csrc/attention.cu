@@ -278,7 +278,7 @@ attention_decode_kernel(const AttnParams p) {
   const int tiles_per = (tiles_total + p.nsplit - 1) / p.nsplit;
   const int tile0 = split * tiles_per, tile1 = min(tiles_total, tile0 + tiles_per);
 
-  const T *qrow = reinterpret_cast<const T *>(p.q) + b * p.q_bs + h * D;
+  const T *qrow = reinterpret_cast<const T *>(p.q) + b * p.q_bs + (long long)(Sk - 1) * p.q_rs + h * D;
   const T *kb = reinterpret_cast<const T *>(p.k) + b * p.k_bs + h * D;
   const T *vb = reinterpret_cast<const T *>(p.v) + b * p.v_bs + h * D;
   const T *mb = p.mask ? reinterpret_cast<const T *>(p.mask) + b * p.mask_bs : nullptr;
@@ -507,14 +507,15 @@ extern "C" size_t eb_attention_decode_scratch_bytes(int batch, int heads, int he
 }
 
 extern "C" int eb_attention_decode(const void *q, const void *k, const void *v, void *out, const void *mask,
-                                   long long q_batch_stride, long long k_batch_stride, long long k_row_stride,
+                                   long long q_batch_stride, long long q_row_stride, long long k_batch_stride,
+                                   long long k_row_stride,
                                    long long v_batch_stride, long long v_row_stride, long long o_batch_stride,
                                    long long mask_batch_stride, int batch, int heads, int kv_len,
                                    const int32_t *kv_len_device, int head_dim, float scale, int dtype, int nsplit,
                                    void *scratch, size_t scratch_bytes, void *stream) {
   AttnParams p{};
   p.q = q; p.k = k; p.v = v; p.o = out; p.mask = mask;
-  p.q_bs = q_batch_stride; p.q_rs = 0; p.k_bs = k_batch_stride; p.k_rs = k_row_stride;
+  p.q_bs = q_batch_stride; p.q_rs = q_row_stride; p.k_bs = k_batch_stride; p.k_rs = k_row_stride;
   p.v_bs = v_batch_stride; p.v_rs = v_row_stride; p.o_bs = o_batch_stride; p.o_rs = 0;
   p.mask_bs = mask_batch_stride;
   p.B = batch; p.H = heads; p.Sq = 1; p.Sk = kv_len; p.kv_len_ptr = kv_len_device; p.causal = 0; p.scale = scale;

@@ -50,6 +50,7 @@ struct GemmParams {
   long long ldc;
   int c_rows_per_batch;          // 0: row m of C is at m*ldc; else (m / rpb)*c_batch_stride + (m % rpb)*ldc
   long long c_batch_stride;
+  const int *c_row_offset_dev;   // optional device scalar: extra row offset of C (rows of ldc), read at run time
   const void *bias;              // [N] or null
   const void *residual;          // [M, N] rows ldr apart, or null
   long long ldr;
@@ -218,8 +219,9 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 }
 
 __device__ __forceinline__ long long c_row_offset(const GemmParams &p, int m) {
-  if (p.c_rows_per_batch <= 0) return (long long)m * p.ldc;
-  return (long long)(m / p.c_rows_per_batch) * p.c_batch_stride + (long long)(m % p.c_rows_per_batch) * p.ldc;
+  const long long extra = p.c_row_offset_dev ? (long long)__ldg(p.c_row_offset_dev) * p.ldc : 0;
+  if (p.c_rows_per_batch <= 0) return (long long)m * p.ldc + extra;
+  return (long long)(m / p.c_rows_per_batch) * p.c_batch_stride + (long long)(m % p.c_rows_per_batch) * p.ldc + extra;
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
@@ -578,8 +580,8 @@ extern "C" int eb_device_status(int *out4, int clear) {
 
 extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
                        const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
-                       int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride, void *workspace,
-                       size_t workspace_bytes, void *stream) {
+                       int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
+                       const int32_t *c_row_offset_device, void *workspace, size_t workspace_bytes, void *stream) {
   EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "gemm: operands must be fp16 or bf16 (got dtype %d)", dtype);
   EB_REQUIRE(out_dtype == dtype || out_dtype == EB_F32, "gemm: output must be the input type or fp32");
   EB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative size");
@@ -598,6 +600,7 @@ extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ld
   p.M = M; p.N = N; p.K = K;
   p.kblocks = (K + kBlockK - 1) / kBlockK;
   p.C = C; p.ldc = ldc; p.c_rows_per_batch = c_rows_per_batch; p.c_batch_stride = c_batch_stride;
+  p.c_row_offset_dev = c_row_offset_device;
   p.bias = bias; p.residual = residual; p.ldr = ldr; p.act = act; p.out_f32 = out_dtype == EB_F32 && dtype != EB_F32;
 
   CUtensorMap tl, tc;

@@ -20,11 +20,12 @@ def workspace(device, nbytes):
 
 
 def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out_rows_per_batch=0,
-         out_batch_stride=0, out_ld=None):
+         out_batch_stride=0, out_ld=None, out_row_offset_device=None):
     """a [M,K] (row stride allowed), w [N,K]; returns out [M,N].
 
     `out`, if given, receives the result; with out_rows_per_batch > 0 row m is written at
-    element (m // rpb) * out_batch_stride + (m % rpb) * out_ld of `out` (a view into a cache)."""
+    element (m // rpb) * out_batch_stride + (m % rpb) * out_ld of `out` (a view into a cache);
+    out_row_offset_device (int32 device scalar) adds that many rows of out_ld at run time."""
     require_cuda(a, w, bias, residual, out)
     if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1]:
         raise RuntimeError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T do not match")
@@ -48,7 +49,8 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
     ws = workspace(a.device, nbytes) if nbytes else None
     check(lib().eb_gemm(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out_ld, ptr(bias), ptr(residual),
                         residual.stride(0) if residual is not None else 0, M, N, K, dtype_code(a.dtype),
-                        dtype_code(out_dtype), code, out_rows_per_batch, out_batch_stride, ptr(ws),
+                        dtype_code(out_dtype), code, out_rows_per_batch, out_batch_stride,
+                        ptr(out_row_offset_device), ptr(ws),
                         ws.numel() if ws is not None else 0, stream_ptr()), "gemm")
     return out
 

@@ -90,11 +90,14 @@ class MultiHeadAttention1D(nn.Module):
             self._packed_w, self._packed_b = w, b
         return self._packed_w, self._packed_b
 
-    def forward(self, hidden_states, attention_mask=None, first_cache=False, seq_lens=None, residual=None):
+    def forward(self, hidden_states, attention_mask=None, first_cache=False, seq_lens=None, residual=None,
+                kv_state=None):
         """hidden_states [batch, seq, hidden].  attention_mask: additive, [batch, 1, 1, kv_len]
         (0 / -10000), or None.  With a cache, first_cache=True runs the whole prompt and any
         later call appends the last position.  `residual`, if given, is added to the output
-        inside the projection's epilogue (the block's skip connection)."""
+        inside the projection's epilogue (the block's skip connection).  `kv_state`, used when a
+        generation step is captured in a CUDA graph, is a device int32 pair [position, length]
+        that the kernels read instead of host values; the cache must already have room."""
         B, S, _ = hidden_states.shape
         hl, d = self.local_hidden, self.attention_head_size
         w, b = self._packed()
@@ -118,14 +121,23 @@ class MultiHeadAttention1D(nn.Module):
             res = residual
         else:
             x = hidden_states[:, -1, :]
-            pos = cache.len
-            cache.ensure(B, pos + 1, 3 * hl, x.dtype, x.device)
-            buf = cache.buf
-            gemm(x, w, bias=b, out=buf[:, pos:], out_rows_per_batch=1, out_batch_stride=buf.stride(0),
-                 out_ld=buf.stride(1))
-            cache.len = kv_len = pos + 1
             mask = attention_mask.reshape(B, -1) if attention_mask is not None else None
-            ctx = attention_decode(buf[:, pos, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, kv_len, mask=mask,
-                                   scale=self.scaling).view(B, 1, hl)
+            if kv_state is None:
+                pos = cache.len
+                cache.ensure(B, pos + 1, 3 * hl, x.dtype, x.device)
+                buf = cache.buf
+                gemm(x, w, bias=b, out=buf[:, pos:], out_rows_per_batch=1, out_batch_stride=buf.stride(0),
+                     out_ld=buf.stride(1))
+                cache.len = kv_len = pos + 1
+                ctx = attention_decode(buf[:, :, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, kv_len, mask=mask,
+                                       scale=self.scaling, q_in_cache=True)
+            else:
+                buf = cache.buf
+                cap = buf.shape[1]
+                gemm(x, w, bias=b, out=buf, out_rows_per_batch=1, out_batch_stride=buf.stride(0), out_ld=buf.stride(1),
+                     out_row_offset_device=kv_state[0:1])
+                ctx = attention_decode(buf[:, :, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, cap, mask=mask,
+                                       scale=self.scaling, q_in_cache=True, kv_len_device=kv_state[1:2])
+            ctx = ctx.view(B, 1, hl)
             res = residual[:, -1:, :] if residual is not None else None
         return self.dense(ctx, residual=res)

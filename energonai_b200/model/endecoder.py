@@ -37,7 +37,7 @@ class Block1D(nn.Module):
         self.mlp = MLP1D(hidden_size=hidden_size, mlp_ratio=mlp_ratio, activation=activation, dtype=dtype, bias=bias,
                          disable_past_cache=disable_past_cache)
 
-    def forward(self, hidden_states, attention_mask=None, first_cache=False, seq_lens=None):
+    def forward(self, hidden_states, attention_mask=None, first_cache=False, seq_lens=None, kv_state=None):
         """Prompt pass (first_cache=True, or no cache): [batch, seq, hidden] -> same shape.
         Generation step: only the last position of the input is used and [batch, 1, hidden] is
         returned (a caller may pass either the whole sequence, as the reference's generation
@@ -46,7 +46,8 @@ class Block1D(nn.Module):
             hidden_states = hidden_states[:, -1:, :]
         normed = self.norm1(hidden_states)
         residual = normed if self.apply_post_layernorm else hidden_states
-        hidden_states = self.attn(normed, attention_mask=attention_mask, first_cache=first_cache, residual=residual)
+        hidden_states = self.attn(normed, attention_mask=attention_mask, first_cache=first_cache, residual=residual,
+                                  kv_state=kv_state)
         normed = self.norm2(hidden_states)
         residual = normed if self.apply_post_layernorm else hidden_states
         return self.mlp(normed, first_cache=True, residual=residual)

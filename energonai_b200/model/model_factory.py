@@ -48,6 +48,7 @@ class PipelineModel(nn.Module):
         self.max_seq_len, self.model_name = max_seq_len, model_name
         self.disable_past_cache = disable_past_cache
         self.eos_token_id = 50256          # the reference hard-codes this stop id (model_factory.py:133)
+        self.use_cuda_graph = True         # greedy generation steps are captured once and replayed
         if first:
             self.embed = Embedding1D(hidden_size=hidden_size, vocab_size=vocab_size, max_seq_len=max_seq_len,
                                      num_tokentypes=num_tokentypes, padding_idx=padding_idx, dtype=dtype,
@@ -69,6 +70,31 @@ class PipelineModel(nn.Module):
         for blk in self.blocks:
             blk.attn.past_cache.reserve = max(1, int(new_tokens))
 
+    # One generation step with every position-dependent quantity read from device memory, so
+    # that the same sequence of launches can be captured once and replayed.
+    def _static_step(self, st):
+        pos_long = st["kv_state"][0:1].to(torch.long)
+        hidden = self.embed.word_embeddings(st["tok"].view(-1, 1)) + self.embed.position_embeddings(pos_long).unsqueeze(0)
+        for block in self.blocks:
+            hidden = block(hidden_states=hidden, attention_mask=st["mask4"], first_cache=False, kv_state=st["kv_state"])
+        logits = self.head(self.norm(hidden))[:, -1, :]
+        tok = logits.argmax(-1)
+        st["out_ids"].index_copy_(1, pos_long, tok.view(-1, 1))
+        st["tok"].copy_(tok)
+        st["kv_state"].add_(1)
+
+    def _graph_state(self, batch_size, tgt_len, model_dtype, dev, ids_dtype):
+        key = (batch_size, tgt_len, model_dtype, ids_dtype, tuple(b.attn.past_cache.buf.data_ptr() for b in self.blocks))
+        st = getattr(self, "_decode_state", None)
+        if st is None or st["key"] != key:
+            add_mask = torch.zeros((batch_size, tgt_len), dtype=model_dtype, device=dev)
+            st = {"key": key, "graph": None, "add_mask": add_mask, "mask4": add_mask.view(batch_size, 1, 1, tgt_len),
+                  "out_ids": torch.empty((batch_size, tgt_len), dtype=ids_dtype, device=dev),
+                  "tok": torch.empty((batch_size,), dtype=ids_dtype, device=dev),
+                  "kv_state": torch.zeros(2, dtype=torch.int32, device=dev)}
+            self._decode_state = st
+        return st
+
     @torch.inference_mode()
     def forward(self, hidden_states=None, input_ids=None, attention_mask=None, seq_lens=None,
                 max_tokens: Optional[int] = None, top_k: Optional[int] = None, top_p: Optional[float] = None,
@@ -80,37 +106,90 @@ class PipelineModel(nn.Module):
         if attention_mask is None:
             attention_mask = torch.ones_like(input_ids)
         dev = input_ids.device
-        model_dtype = self.norm.module.weight.dtype if self.last else self.blocks[0].norm1.module.weight.dtype
+        model_dtype = self.norm.module.weight.dtype
         self.reserve_cache(tgt_len - cur_len)
-        # additive key mask for every position the sequence may reach: (1 - mask) * -10000, then 0
-        add_mask = torch.zeros((batch_size, tgt_len), dtype=model_dtype, device=dev)
-        add_mask[:, :cur_len] = (1.0 - attention_mask.view(batch_size, -1).to(model_dtype)) * -10000.0
-        out_ids = torch.empty((batch_size, tgt_len), dtype=input_ids.dtype, device=dev)
-        out_ids[:, :cur_len] = input_ids
         greedy = top_k == 1 and (temperature is None or temperature > 0)
-        step_ids, past = input_ids, 0
-        first_cache = True
-        tok = None
-        for pos in range(cur_len, tgt_len):
-            hidden_states = self.embed(step_ids, past_key_values_length=past) if self.first else hidden_states
-            mask4 = add_mask[:, :pos].view(batch_size, 1, 1, pos)
-            if self.disable_past_cache and not first_cache:
-                hidden_states = self.embed(out_ids[:, :pos])
-            for block in self.blocks:
-                hidden_states = block(hidden_states=hidden_states, attention_mask=mask4, first_cache=first_cache)
-            if self.last:
-                last_hidden = self.norm(hidden_states[:, -1:, :].contiguous())
+        step_times = record.setdefault("step_events", []) if record is not None else None
+        from .. import _lib
+        launches0, replayed = _lib.launch_count, 0
+
+        def mark():
+            if step_times is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                step_times.append(ev)
+
+        # ---- prompt pass ----
+        add_mask_prompt = (1.0 - attention_mask.view(batch_size, -1).to(model_dtype)) * -10000.0
+        mark()
+        hidden_states = self.embed(input_ids)
+        mask4 = add_mask_prompt.view(batch_size, 1, 1, cur_len)
+        for block in self.blocks:
+            hidden_states = block(hidden_states=hidden_states, attention_mask=mask4, first_cache=True)
+        last_hidden = self.norm(hidden_states[:, -1:, :].contiguous())
+        logits = self.head(last_hidden)[:, -1, :]
+        if record is not None:
+            record.setdefault("logits", []).append(logits.clone())
+            record.setdefault("hidden", []).append(last_hidden[:, -1, :].clone())
+        tok = logits.argmax(-1) if greedy else self.generate(input_ids, logits, top_k=top_k, top_p=top_p,
+                                                             temperature=temperature)
+        mark()
+        if not max_tokens:
+            return tok
+        if torch.all(tok == self.eos_token_id):
+            return input_ids
+
+        # ---- generation steps ----
+        st = self._graph_state(batch_size, tgt_len, model_dtype, dev, input_ids.dtype)
+        st["add_mask"].zero_()
+        st["add_mask"][:, :cur_len] = add_mask_prompt
+        out_ids = st["out_ids"]
+        out_ids[:, :cur_len] = input_ids
+        out_ids[:, cur_len] = tok
+        st["tok"].copy_(tok)
+        st["kv_state"].copy_(torch.tensor([cur_len, cur_len + 1], dtype=torch.int32), non_blocking=False)
+        use_graph = greedy and self.use_cuda_graph and (record is None or record.get("allow_graph", False))
+        produced = cur_len + 1
+        for pos in range(cur_len + 1, tgt_len):
+            if use_graph:
+                if st["graph"] is None and pos == cur_len + 1:
+                    before = _lib.launch_count
+                    self._static_step(st)                      # eager once: also warms every kernel up
+                    st["launches"] = _lib.launch_count - before
+                elif st["graph"] is None:
+                    g = torch.cuda.CUDAGraph()
+                    before = _lib.launch_count
+                    with torch.cuda.graph(g):
+                        self._static_step(st)
+                    launches0 += _lib.launch_count - before    # captured, not executed
+                    st["graph"] = g
+                    g.replay()
+                    replayed += st["launches"]
+                else:
+                    st["graph"].replay()
+                    replayed += st["launches"]
+                tok = st["tok"]
+            else:
+                hidden_states = self.embed(tok.view(-1, 1), past_key_values_length=pos - 1)
+                mask4 = st["add_mask"][:, :pos].view(batch_size, 1, 1, pos)
+                for block in self.blocks:
+                    hidden_states = block(hidden_states=hidden_states, attention_mask=mask4, first_cache=False)
+                last_hidden = self.norm(hidden_states)
                 logits = self.head(last_hidden)[:, -1, :]
                 if record is not None:
                     record.setdefault("logits", []).append(logits.clone())
                     record.setdefault("hidden", []).append(last_hidden[:, -1, :].clone())
                 tok = logits.argmax(-1) if greedy else self.generate(out_ids[:, :pos], logits, top_k=top_k, top_p=top_p,
                                                                      temperature=temperature)
+                out_ids[:, pos] = tok
+            mark()
             if torch.all(tok == self.eos_token_id):
-                return out_ids[:, :pos] if max_tokens else tok
-            out_ids[:, pos] = tok
-            step_ids, past, first_cache = tok.view(-1, 1), pos, False
-        return out_ids if max_tokens else tok
+                break
+            produced = pos + 1
+        for blk in self.blocks:                                # host bookkeeping of the cache length
+            blk.attn.past_cache.len = produced - 1
+        self.launches_last_call = _lib.launch_count - launches0 + replayed   # kernels of this library executed
+        return out_ids[:, :produced].clone()
 
     def get_logits_processor(self, top_k=None, top_p=None, temperature=None):
         from transformers.generation import (LogitsProcessorList, TemperatureLogitsWarper, TopKLogitsWarper,

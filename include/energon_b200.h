@@ -145,6 +145,9 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
  *   Row m of C starts at element m*ldc, or, when c_rows_per_batch > 0, at
  *   (m / c_rows_per_batch)*c_batch_stride + (m % c_rows_per_batch)*ldc  (this lets a
  *   projection write straight into a [batch, max_len, width] cache at a position offset).
+ *   c_row_offset_device, if non-NULL, is a device int32 read by the kernel: that many further
+ *   rows (of ldc elements) are added to every row's offset, so a captured launch can append
+ *   at a position that advances between replays.
  *   K, N, all leading dimensions and c_batch_stride must be multiples of 8, pointers 16-byte
  *   aligned.
  * For M <= 128 (decode) the kernel streams W once, split evenly over all SMs, and combines
@@ -153,7 +156,8 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
  * share a workspace must not overlap on the device.  workspace may be NULL for M > 128. */
 EB_API int eb_gemm(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc, const void *bias,
             const void *residual, long long ldr, int M, int N, int K, int dtype, int out_dtype, int act,
-            int c_rows_per_batch, long long c_batch_stride, void *workspace, size_t workspace_bytes, void *stream);
+            int c_rows_per_batch, long long c_batch_stride, const int32_t *c_row_offset_device, void *workspace,
+            size_t workspace_bytes, void *stream);
 EB_API size_t eb_gemm_workspace_bytes(int M, int N, int K);
 
 /* ---- fused attention ----------------------------------------------------------------------- */
@@ -176,15 +180,17 @@ EB_API int eb_attention_prefill(const void *q, const void *k, const void *v, voi
 
 /* The same product for one new query row per sequence against the cached keys/values (the
  * generation step; replaces the torch.cat past_cache reads of attention.py:86-98 followed by
- * attention.py:105-124).  q[b] is one row (base + b*q_batch_stride + h*head_dim); all kv_len
- * cached keys are visible.  kv_len_device, if non-NULL, is a device int32 that overrides
+ * attention.py:105-124).  q[b] is the row at base + b*q_batch_stride + (kv_len-1)*q_row_stride +
+ * h*head_dim: q_row_stride 0 for a plain [batch, heads*head_dim] tensor, or the cache row
+ * stride when the query projection sits in the cache row of the new token.  All kv_len cached
+ * keys are visible.  kv_len_device, if non-NULL, is a device int32 that overrides
  * kv_len at run time (so a captured launch can be replayed while the cache grows).  The key
  * range is split over `nsplit` CTAs per (sequence, head); for nsplit > 1 `scratch` must hold
  * eb_attention_decode_scratch_bytes(...) bytes, 16-byte aligned, zero-filled once before
  * first use.  Calls sharing a scratch must not overlap on the device. */
 EB_API int eb_attention_decode(const void *q, const void *k, const void *v, void *out, const void *mask,
-                        long long q_batch_stride, long long k_batch_stride, long long k_row_stride,
-                        long long v_batch_stride, long long v_row_stride, long long o_batch_stride,
+                        long long q_batch_stride, long long q_row_stride, long long k_batch_stride,
+                        long long k_row_stride, long long v_batch_stride, long long v_row_stride, long long o_batch_stride,
                         long long mask_batch_stride, int batch, int heads, int kv_len, const int32_t *kv_len_device,
                         int head_dim, float scale, int dtype, int nsplit, void *scratch, size_t scratch_bytes,
                         void *stream);

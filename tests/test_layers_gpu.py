@@ -166,3 +166,24 @@ def test_sampling_path_runs():
     assert out.shape == (2, 12) and torch.equal(out[:, :8], ids)
     nxt = model(input_ids=ids, attention_mask=torch.ones(2, 8, device="cuda"), top_k=1)
     assert nxt.shape == (2,)
+
+
+def test_graph_replayed_generation_equals_eager():
+    """Greedy generation with the captured-and-replayed step (the default) gives the same
+    tokens as the eager step, and a second call reuses the captured graph."""
+    from energonai_b200.model import create_pipeline_model
+    c = mg.TINY
+    torch.manual_seed(0)
+    model = create_pipeline_model(depth=2, vocab_size=c["vocab"], hidden_size=c["hidden"], max_seq_len=c["max_pos"],
+                                  num_heads=c["heads"], activation=torch.nn.functional.relu, fused_qkv=False,
+                                  dtype=torch.float16)
+    ids = torch.randint(2, c["vocab"], (3, 10), device="cuda")
+    mask = torch.ones(3, 10, device="cuda")
+    mask[1, :4] = 0
+    out_graph = model(input_ids=ids, attention_mask=mask, max_tokens=30, top_k=1)
+    assert model._decode_state["graph"] is not None
+    out_again = model(input_ids=ids, attention_mask=mask, max_tokens=30, top_k=1)
+    model.use_cuda_graph = False
+    out_eager = model(input_ids=ids, attention_mask=mask, max_tokens=30, top_k=1)
+    assert out_graph.shape == (3, 30)
+    assert torch.equal(out_graph, out_eager) and torch.equal(out_graph, out_again)
