@@ -44,10 +44,11 @@ def attention_prefill(q, k, v, head_dim, mask=None, causal=True, scale=None, out
 
 
 def pick_nsplit(batch, heads, kv_len, sm_count=148):
-    """Enough CTAs for two per SM, at most one per 64-key tile."""
+    """Split the key range so that the grid is at least four waves of the three CTAs an SM
+    holds (short tails), without going below two 64-key tiles per CTA."""
     tiles = max(1, (kv_len + 63) // 64)
-    want = -(-2 * sm_count // max(1, batch * heads))
-    return max(1, min(want, tiles, 64))
+    want = -(-4 * 3 * sm_count // max(1, batch * heads))
+    return max(1, min(want, max(1, tiles // 2), 64))
 
 
 def attention_decode(q, k, v, head_dim, kv_len, mask=None, scale=None, out=None, nsplit=None, kv_len_device=None,

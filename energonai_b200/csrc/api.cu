@@ -1,6 +1,7 @@
 // Error reporting and device queries behind the C ABI.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -35,6 +36,15 @@ int sm_count() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+bool pdl_enabled() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char *e = getenv("EB_PDL");
+    cached = (e && e[0] == '0') ? 0 : 1;
+  }
+  return cached == 1;
 }
 
 }  // namespace eb

@@ -110,6 +110,8 @@ attention_prefill_kernel(const AttnParams p) {
   const uint32_t q_s = smem_u32(smem), k_s = q_s + kTileBytes, v_s = k_s + 2 * kTileBytes;
   float *mask_s = reinterpret_cast<float *>(smem + 5 * kTileBytes);   // [2][kBN]
 
+  griddep_wait();
+  griddep_launch();
   const int qt = gridDim.x - 1 - blockIdx.x;   // heavy (late) causal tiles first
   const int h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -271,6 +273,8 @@ attention_decode_kernel(const AttnParams p) {
   float *red = mask_s + 2 * kBN;                                               // [4][D + 2] warp partials
   __shared__ int s_last;
 
+  griddep_wait();
+  griddep_launch();
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int Sk = p.kv_len_ptr ? *p.kv_len_ptr : p.Sk;
@@ -438,7 +442,7 @@ template <typename T, int D> int launch_prefill(const AttnParams &p, cudaStream_
     configured[dev] = true;
   }
   dim3 grid((p.Sq + kBM - 1) / kBM, p.H, p.B);
-  kern<<<grid, kThreads, smem, st>>>(p);
+  launch_pdl(kern, grid, dim3(kThreads), smem, st, p);
   return check_launch("attention_prefill");
 }
 
@@ -456,7 +460,7 @@ template <typename T, int D> int launch_decode(const AttnParams &p, cudaStream_t
     configured[dev] = true;
   }
   dim3 grid(p.nsplit, p.H, p.B);
-  kern<<<grid, kThreads, smem, st>>>(p);
+  launch_pdl(kern, grid, dim3(kThreads), smem, st, p);
   return check_launch("attention_decode");
 }
 

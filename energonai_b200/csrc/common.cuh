@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "../../include/energon_b200.h"
 
 namespace eb {
@@ -26,6 +28,31 @@ inline bool dtype_ok(int dtype) { return dtype == EB_F32 || dtype == EB_F16 || d
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
 int sm_count();   // multiprocessors of the current device (cached per device)
+bool pdl_enabled();   // programmatic dependent launch (on unless the environment sets EB_PDL=0)
+
+// Launch with programmatic stream serialization: the kernel may start while its predecessor
+// in the stream is still draining, and must execute griddep_wait() before it touches anything
+// the predecessor wrote.  Work that only reads constants (weights) can be issued before that.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
+// Wait for the preceding kernel of the stream (complete and visible); no-op for a plain launch.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Allow the following kernel of the stream to begin launching.
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- dtype conversion ---------------------------------------------------------------------
 template <typename T> __device__ __forceinline__ float to_f32(T v);

@@ -4,14 +4,15 @@
 // tensor memory.  One kernel template serves two orientations:
 //
 //   normal (M > 128): TMEM lanes = 128 rows of A, TMEM columns = BN rows of W.  Persistent
-//       CTAs walk output tiles in a grouped raster so that concurrently running CTAs share
-//       A and W panels in L2.
-//   swapped (M <= 128, decode): TMEM lanes = 128 rows of W, TMEM columns = the (padded) M
-//       rows of A.  The work is weight streaming, so it is cut stream-K style: the
-//       (tile, k-block) space is divided into equal contiguous ranges, one per CTA, every SM
-//       pulls the same number of weight bytes, and tiles shared by several CTAs are reduced
-//       through fp32 partials in a caller-provided workspace by whichever CTA arrives last
-//       (fixed summation order, so results are deterministic).
+//       CTAs walk 128 x BN output tiles in a grouped raster so that concurrently running CTAs
+//       share A and W panels in L2.
+//   swapped (M <= 128, generation steps): TMEM lanes = 128 rows of W, TMEM columns = the (padded)
+//       M rows of A.  The work is one pass over W (HBM-bound).  An MMA over 128 lanes costs the
+//       same however many lanes carry useful rows, so W is always taken in full 128-row tiles,
+//       and the (tile, k) space is cut stream-K style into equal contiguous ranges, one per CTA:
+//       every SM pulls the same number of weight bytes.  A tile shared by several CTAs is
+//       reduced through fp32 partials in a caller-provided workspace by whichever CTA arrives
+//       last, summing in a fixed order, so results are deterministic.
 //
 // Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM allocation and
 // tcgen05.mma issue (one lane), warps 2-5 = epilogue (tcgen05.ld -> bias / activation /
@@ -19,12 +20,17 @@
 // transaction bytes; empty: tcgen05.commit), and two TMEM accumulators are ping-ponged so the
 // epilogue of one tile overlaps the main loop of the next.
 //
+// The kernel is launched with programmatic stream serialization: its prologue and the first
+// weight tiles (which never depend on the preceding kernel) are issued before
+// griddepcontrol.wait; only the activation tiles and the epilogue wait for the predecessor.
+//
 // Every mbarrier wait is bounded by a wall-clock budget.  When it expires the CTA records
 // where it gave up in a device status word (eb_device_status), raises a CTA-wide abort flag so
 // the other roles leave their loops, lets in-flight copies land, frees its tensor memory and
 // returns; the context stays usable.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -38,7 +44,8 @@ constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
 constexpr int kGroup = 16;       // raster group height (lane-side tiles) in normal mode
 constexpr unsigned long long kWaitBudgetNs = 1000ull * 1000ull * 1000ull;
-constexpr size_t kCounterBytes = 64 * 1024;   // workspace head: one int per lane-side tile, zero between calls
+constexpr int kMaxStages = 32;
+constexpr uint32_t kBarrierBytes = 1024;      // head of shared memory: mbarriers, TMEM slot, abort flag
 
 __device__ int g_status[4];      // [0] code (0 = ok), [1] where, [2] block, [3] detail
 
@@ -56,9 +63,12 @@ struct GemmParams {
   long long ldr;
   int act;
   int out_f32;                   // 1: C is fp32, else the input type
-  float *partial;                // stream-K partials (swap mode)
-  int *counters;                 // one per lane-side tile (swap mode), zero between calls
-  long long units_per_cta;       // stream-K: (tile, k-block) units per CTA
+  float *partial;                // swap mode: stream-K partial sums [cta][2][BN][128]
+  int *counters;                 // swap mode: one arrival counter per 128-row tile, zero between calls
+  long long units_per_cta;       // swap mode: stream-K units (one unit = one pipeline stage of one tile) per CTA
+  int stages;                    // pipeline depth actually used (<= kMaxStages)
+  int kpb;                       // k-blocks (64 columns each) per pipeline stage / barrier hand-over
+  int static_w;                  // W may be read before the preceding kernel of the stream has finished
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -158,23 +168,26 @@ __host__ __device__ constexpr uint32_t make_idesc(int n, int is_bf16) {
 
 // ---- work decomposition -----------------------------------------------------------------------
 struct Segment {
-  int lane_tile, col_tile;   // tile coordinates (lane-side, column-side)
-  int kb0, kb1;              // k-block range
+  int lane_row0;             // first row of the lane-side operand
+  int lane_tile;             // its tile index
+  int col_tile;              // tile index of the column-side operand
+  int sk0, sk1;              // range of pipeline stages (kpb k-blocks each) of this tile
   bool partial;              // covers only part of K (swap mode)
   int which;                 // 0: first segment of this CTA's range, 1: a later one
 };
 
 template <int BN, bool SWAP> struct Scheduler {
   const GemmParams &p;
-  int lane_tiles, col_tiles;
-  long long pos, end;        // SWAP: unit range of this CTA;  normal: tile index / total tiles
+  int lane_tiles, col_tiles, nsk;
+  long long pos, end;
   bool first;
   __device__ Scheduler(const GemmParams &pp) : p(pp) {
     lane_tiles = (p.lane_rows + kLanes - 1) / kLanes;
-    col_tiles = (p.col_rows + BN - 1) / BN;
+    col_tiles = SWAP ? 1 : (p.col_rows + BN - 1) / BN;
+    nsk = (p.kblocks + p.kpb - 1) / p.kpb;
     first = true;
     if (SWAP) {
-      const long long total = (long long)lane_tiles * p.kblocks;   // col_tiles == 1 in swap mode
+      const long long total = (long long)lane_tiles * nsk;
       pos = (long long)blockIdx.x * p.units_per_cta;
       end = pos + p.units_per_cta < total ? pos + p.units_per_cta : total;
     } else {
@@ -185,14 +198,14 @@ template <int BN, bool SWAP> struct Scheduler {
   __device__ bool next(Segment &s) {
     if (pos >= end) return false;
     if (SWAP) {
-      s.lane_tile = (int)(pos / p.kblocks);
+      s.lane_tile = (int)(pos / nsk);
       s.col_tile = 0;
-      s.kb0 = (int)(pos % p.kblocks);
+      s.sk0 = (int)(pos % nsk);
       const long long left = end - pos;
-      s.kb1 = (long long)s.kb0 + left < p.kblocks ? (int)(s.kb0 + left) : p.kblocks;
-      s.partial = !(s.kb0 == 0 && s.kb1 == p.kblocks);
+      s.sk1 = (long long)s.sk0 + left < nsk ? (int)(s.sk0 + left) : nsk;
+      s.partial = !(s.sk0 == 0 && s.sk1 == nsk);
       s.which = first ? 0 : 1;
-      pos += s.kb1 - s.kb0;
+      pos += s.sk1 - s.sk0;
     } else {
       const int per_group = kGroup * col_tiles;
       const int group = (int)(pos / per_group), in_group = (int)(pos % per_group);
@@ -200,12 +213,13 @@ template <int BN, bool SWAP> struct Scheduler {
       const int gsz = lane_tiles - first_lane < kGroup ? lane_tiles - first_lane : kGroup;
       s.lane_tile = first_lane + in_group % gsz;
       s.col_tile = in_group / gsz;
-      s.kb0 = 0;
-      s.kb1 = p.kblocks;
+      s.sk0 = 0;
+      s.sk1 = nsk;
       s.partial = false;
       s.which = 0;
       pos += gridDim.x;
     }
+    s.lane_row0 = s.lane_tile * kLanes;
     first = false;
     return true;
   }
@@ -225,28 +239,35 @@ __device__ __forceinline__ long long c_row_offset(const GemmParams &p, int m) {
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------
-template <typename T, int BN, int STAGES, bool SWAP>
+// Shared memory: [1 KB: mbarriers, TMEM slot, flags][stages x kpb x (lane tile | column tile)].
+template <typename T, int BN, bool SWAP>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__ CUtensorMap tm_col, const GemmParams p) {
-  constexpr uint32_t kLaneBytes = kLanes * 128, kColBytes = BN * 128, kStageBytes = kLaneBytes + kColBytes;
+  constexpr uint32_t kColBytes = BN * 128;
   constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
-  constexpr uint32_t kIdesc = make_idesc(BN, sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0);
+  constexpr uint32_t kIdesc = make_idesc(BN, std::is_same<T, __nv_bfloat16>::value ? 1 : 0);
+  constexpr uint32_t lane_bytes = kLanes * 128u;
+  const uint32_t sub_bytes = lane_bytes + kColBytes;      // one k-block: lane tile | column tile
+  const uint32_t stage_bytes = sub_bytes * (uint32_t)p.kpb;
+  const int stages = p.stages, kpb = p.kpb;
+  const int nsk = (p.kblocks + kpb - 1) / kpb;             // stages' worth of K per output tile
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t *smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  const uint32_t tiles_addr = smem_u32(smem);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * kStageBytes);
-  const uint32_t full_bar = smem_u32(bars), empty_bar = full_bar + 8 * STAGES;
-  const uint32_t tfull_bar = empty_bar + 8 * STAGES, tempty_bar = tfull_bar + 16, epi_bar = tempty_bar + 16;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+  const uint32_t full_bar = smem_u32(bars), empty_bar = full_bar + 8 * kMaxStages;
+  const uint32_t tfull_bar = empty_bar + 8 * kMaxStages, tempty_bar = tfull_bar + 16;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kMaxStages + 5);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   volatile int *last_flag = reinterpret_cast<volatile int *>(tmem_slot + 2);   // two entries, alternating
+  const uint32_t epi_bar = tempty_bar + 16;
+  const uint32_t tiles_addr = smem_u32(smem) + kBarrierBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
     }
@@ -272,29 +293,77 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  griddep_launch();   // the next kernel of the stream may become resident and run its own prologue
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      Scheduler<BN, SWAP> sched(p);
+    // ---------------- TMA producer (whole warp; lane j moves k-block j of every stage) ----------------
+    // A single thread issuing every copy was the bottleneck of the weight-streaming case (its
+    // dependent instruction chain per stage took longer than the stage's bytes need at HBM
+    // speed), so the k-blocks of a stage are spread over lanes and the per-stage bookkeeping
+    // (barrier wait, expected byte count) is done once by lane 0.
+    //
+    // When the caller declares the weights static (they do not depend on the preceding kernel
+    // of the stream), the weight tiles of the first `stages` stages are requested before
+    // waiting for that kernel; activations always follow the wait.
+    const CUtensorMap *tm_w = SWAP ? &tm_lane : &tm_col;
+    const CUtensorMap *tm_x = SWAP ? &tm_col : &tm_lane;
+    const uint32_t w_off = lane * sub_bytes + (SWAP ? 0u : lane_bytes);
+    const uint32_t x_off = lane * sub_bytes + (SWAP ? lane_bytes : 0u);
+    const bool mover = lane < kpb;
+    const uint32_t movers_mask = kpb >= 32 ? 0xffffffffu : ((1u << kpb) - 1u);
+    if (mover) {
+    const int last_valid = p.kblocks - (nsk - 1) * kpb;                   // k-blocks in the last stage of a tile
+    const uint32_t full_tx = stage_bytes, last_tx = (uint32_t)last_valid * sub_bytes;
+    int pre = 0;
+    if (!p.static_w) griddep_wait();
+    {
+      Scheduler<BN, SWAP> sw(p);
       Segment s;
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      while (ok && sched.next(s)) {
-        for (int kb = s.kb0; kb < s.kb1; ++kb) {
-          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, 1)) { ok = false; break; }
-          const uint32_t fb = full_bar + 8 * stage;
-          mbar_expect_tx(fb, kStageBytes);
-          const uint32_t dst = tiles_addr + stage * kStageBytes;
-          tma_load_2d(dst, &tm_lane, fb, kb * kBlockK, s.lane_tile * kLanes);
-          tma_load_2d(dst + kLaneBytes, &tm_col, fb, kb * kBlockK, s.col_tile * BN);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      while (pre < stages && sw.next(s)) {
+        const int w_row = SWAP ? s.lane_row0 : s.col_tile * BN;
+        for (int sk = s.sk0; sk < s.sk1 && pre < stages; ++sk, ++pre) {
+          const uint32_t fb = full_bar + 8 * pre;
+          if (lane == 0) mbar_expect_tx(fb, sk == nsk - 1 ? last_tx : full_tx);
+          __syncwarp(movers_mask);
+          const int kb = sk * kpb + lane;
+          if (mover && kb < p.kblocks) tma_load_2d(tiles_addr + pre * stage_bytes + w_off, tm_w, fb, kb * kBlockK, w_row);
         }
       }
     }
+    if (p.static_w) griddep_wait();
+    Scheduler<BN, SWAP> sched(p);
+    Segment s;
+    int stage = 0, iter = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    while (ok && sched.next(s)) {
+      const int w_row = SWAP ? s.lane_row0 : s.col_tile * BN;
+      const int x_row = SWAP ? s.col_tile * BN : s.lane_row0;
+      for (int sk = s.sk0; sk < s.sk1; ++sk, ++iter) {
+        const uint32_t fb = full_bar + 8 * stage;
+        const uint32_t dst = tiles_addr + stage * stage_bytes;
+        const bool fresh = iter >= pre;          // the weight tile was not requested before the wait
+        if (fresh) {
+          int good = 1;
+          if (lane == 0) {
+            good = mbar_wait(empty_bar + 8 * stage, phase ^ 1u, abort_flag, 1) ? 1 : 0;
+            if (good) mbar_expect_tx(fb, sk == nsk - 1 ? last_tx : full_tx);
+          }
+          good = __shfl_sync(movers_mask, good, 0);
+          if (!good) { ok = false; break; }
+        }
+        const int kb = sk * kpb + lane;
+        if (mover && kb < p.kblocks) {
+          if (fresh) tma_load_2d(dst + w_off, tm_w, fb, kb * kBlockK, w_row);
+          tma_load_2d(dst + x_off, tm_x, fb, kb * kBlockK, x_row);
+        }
+        if (++stage == stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    }   // mover lanes
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    griddep_wait();
     if (lane == 0) {
       Scheduler<BN, SWAP> sched(p);
       Segment s;
@@ -305,18 +374,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
         if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1u, abort_flag, 2)) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = s.kb0; kb < s.kb1; ++kb) {
+        for (int sk = s.sk0; sk < s.sk1; ++sk) {
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
           tcgen05_fence_after();
-          const uint32_t a_addr = tiles_addr + stage * kStageBytes;
-          const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + kLaneBytes);
+          for (int j = 0; j < kpb && sk * kpb + j < p.kblocks; ++j) {
+            const uint32_t a_addr = tiles_addr + stage * stage_bytes + j * sub_bytes;
+            const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + lane_bytes);
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            // advancing 16 elements along K inside the swizzle atom = +32 bytes = +2 in the address field
-            tcgen05_mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (kb > s.kb0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+              // advancing 16 elements along K inside the swizzle atom = +32 bytes = +2 in the address field
+              tcgen05_mma_f16(d_tmem, a_desc + 2 * k, b_desc + 2 * k, kIdesc, (sk > s.sk0 || j > 0 || k > 0) ? 1u : 0u);
+            }
           }
           tcgen05_commit(empty_bar + 8 * stage);   // frees the stage once these MMAs have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         tcgen05_commit(tfull_bar + 8 * acc);        // accumulator complete
@@ -325,6 +396,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
     }
   } else {
     // ---------------- epilogue (warps 2..5) ----------------
+    griddep_wait();
     const int quarter = warp & 3;                   // TMEM lane quarter this warp may access
     const int lrow = quarter * 32 + lane;           // lane-side row inside the tile
     const T *bias = reinterpret_cast<const T *>(p.bias);
@@ -348,7 +420,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
       const uint32_t t_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
 
       if (!SWAP) {
-        const int m = s.lane_tile * kLanes + lrow;
+        const int m = s.lane_row0 + lrow;
         const bool m_ok = m < p.M;
         const long long c_off = m_ok ? c_row_offset(p, m) : 0;
 #pragma unroll 1
@@ -404,7 +476,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
         if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
       } else {
         // swapped: this thread owns weight row n, TMEM columns are the batch rows m
-        const int n = s.lane_tile * kLanes + lrow;
+        const int n = s.lane_row0 + lrow;
         const bool n_ok = n < p.N;
         float v[BN];
 #pragma unroll
@@ -419,13 +491,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           float *mine = p.partial + ((size_t)(blockIdx.x * 2 + s.which) * BN) * kLanes;
 #pragma unroll
           for (int m = 0; m < BN; ++m)
-            if (m < p.M) mine[(size_t)m * kLanes + lrow] = v[m];
+            if (m < p.M) __stcg(mine + (size_t)m * kLanes + lrow, v[m]);
           __threadfence();
           if (!epi_sync()) { alive = false; continue; }
           // CTAs whose unit range intersects this tile
-          const long long t0 = (long long)s.lane_tile * p.kblocks;
+          const long long t0 = (long long)s.lane_tile * sched.nsk;
           const int first_cta = (int)(t0 / p.units_per_cta);
-          const int last_cta = (int)((t0 + p.kblocks - 1) / p.units_per_cta);
+          const int last_cta = (int)((t0 + sched.nsk - 1) / p.units_per_cta);
           if (threadIdx.x == 64) {
             const int arrived = atomicAdd(p.counters + s.lane_tile, 1);
             const int is_last = arrived == last_cta - first_cta;
@@ -439,9 +511,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
             __threadfence();
 #pragma unroll
             for (int m = 0; m < BN; ++m) v[m] = 0.f;
+#pragma unroll 2
             for (int cta = first_cta; cta <= last_cta; ++cta) {
               // a CTA's piece of this tile is its first segment iff its range starts inside the tile
-              const int which = ((long long)cta * p.units_per_cta) / p.kblocks == s.lane_tile ? 0 : 1;
+              const int which = ((long long)cta * p.units_per_cta) / sched.nsk == s.lane_tile ? 0 : 1;
               const float *theirs = p.partial + ((size_t)(cta * 2 + which) * BN) * kLanes;
 #pragma unroll
               for (int m = 0; m < BN; ++m)
@@ -516,39 +589,37 @@ int make_map(CUtensorMap *map, const void *base, int dtype, long long rows, long
   return EB_OK;
 }
 
-template <int BN, int STAGES> constexpr size_t smem_bytes() {
-  return (size_t)STAGES * (kLanes * 128 + BN * 128) + (2 * STAGES + 5) * 8 + 16 + 1024;
-}
-
-template <typename T, int BN, int STAGES, bool SWAP>
-int launch(const CUtensorMap &tl, const CUtensorMap &tc, const GemmParams &p, int grid, cudaStream_t st) {
-  auto kern = gemm_kernel<T, BN, STAGES, SWAP>;
-  constexpr size_t smem = smem_bytes<BN, STAGES>();
-  static bool configured[64] = {};
+template <typename T, int BN, bool SWAP>
+int launch(const CUtensorMap &tl, const CUtensorMap &tc, const GemmParams &p, int grid, size_t smem, cudaStream_t st) {
+  auto kern = gemm_kernel<T, BN, SWAP>;
+  static size_t configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+  if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
       cudaGetLastError();
-      return fail(EB_ECUDA, "gemm: cannot reserve %zu bytes of shared memory", smem);
+      return fail(EB_ECUDA, "gemm: cannot reserve shared memory");
     }
-    configured[dev] = true;
+    configured[dev] = 227 * 1024;
   }
-  kern<<<grid, kThreads, smem, st>>>(tl, tc, p);
+  launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, tl, tc, p);
   return check_launch("gemm");
 }
 
 inline int swap_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
 
-// Stream-K split of the swapped orientation: grid and (tile, k-block) units per CTA.
-inline void swap_split(int N, int K, int *grid, long long *units) {
+// Stream-K split of the swapped orientation: grid and units (pipeline stages of a tile) per CTA.
+inline void swap_split(int N, int K, int kpb, int *grid, long long *units) {
   const long long tiles = (N + kLanes - 1) / kLanes, kblocks = (K + kBlockK - 1) / kBlockK;
-  const long long total = tiles * kblocks;
+  const long long nsk = (kblocks + kpb - 1) / kpb;
+  const long long total = tiles * nsk;
   long long g = sm_count();
-  if (g > total / 4) g = total / 4 > 0 ? total / 4 : 1;   // at least 4 k-blocks per CTA
+  if (g > total / 2) g = total / 2 > 0 ? total / 2 : 1;   // at least two stages per CTA
   *units = (total + g - 1) / g;
   *grid = (int)((total + *units - 1) / *units);
 }
+
+constexpr size_t kCounterBytes = 64 * 1024;   // workspace head: one int per 128-row tile, zero between calls
 
 }  // namespace
 }  // namespace eb
@@ -557,10 +628,8 @@ using namespace eb;
 
 extern "C" size_t eb_gemm_workspace_bytes(int M, int N, int K) {
   if (M > kLanes || M <= 0 || N <= 0 || K <= 0) return 0;
-  int grid;
-  long long units;
-  swap_split(N, K, &grid, &units);
-  return kCounterBytes + (size_t)grid * 2 * swap_bn(M) * kLanes * sizeof(float);
+  // the partials are sized for the largest grid (one CTA per SM)
+  return kCounterBytes + (size_t)sm_count() * 2 * swap_bn(M) * kLanes * sizeof(float);
 }
 
 extern "C" int eb_device_status(int *out4, int clear) {
@@ -581,11 +650,13 @@ extern "C" int eb_device_status(int *out4, int clear) {
 extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
                        const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
                        int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
-                       const int32_t *c_row_offset_device, void *workspace, size_t workspace_bytes, void *stream) {
+                       const int32_t *c_row_offset_device, int flags, void *workspace, size_t workspace_bytes,
+                       void *stream) {
   EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "gemm: operands must be fp16 or bf16 (got dtype %d)", dtype);
   EB_REQUIRE(out_dtype == dtype || out_dtype == EB_F32, "gemm: output must be the input type or fp32");
   EB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative size");
   EB_REQUIRE(act >= EB_ACT_NONE && act <= EB_ACT_GELU_ERF, "gemm: unknown activation %d", act);
+  EB_REQUIRE((flags & ~EB_GEMM_STATIC_W) == 0, "gemm: unknown flag bits 0x%x", flags);
   if (M == 0 || N == 0) return EB_OK;
   EB_REQUIRE(A && W && C, "gemm: null operand");
   EB_REQUIRE(K >= 8 && K % 8 == 0 && N % 8 == 0, "gemm: K and N must be positive multiples of 8 (K=%d N=%d)", K, N);
@@ -601,6 +672,7 @@ extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ld
   p.kblocks = (K + kBlockK - 1) / kBlockK;
   p.C = C; p.ldc = ldc; p.c_rows_per_batch = c_rows_per_batch; p.c_batch_stride = c_batch_stride;
   p.c_row_offset_dev = c_row_offset_device;
+  p.static_w = (flags & EB_GEMM_STATIC_W) ? 1 : 0;
   p.bias = bias; p.residual = residual; p.ldr = ldr; p.act = act; p.out_f32 = out_dtype == EB_F32 && dtype != EB_F32;
 
   CUtensorMap tl, tc;
@@ -609,7 +681,19 @@ extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ld
     // swapped orientation: lanes = rows of W, columns = rows of A
     const int bn = swap_bn(M);
     int grid;
-    swap_split(N, K, &grid, &p.units_per_cta);
+    // k-blocks per stage: stages of about 36 KB keep the hand-over count per byte low
+    const size_t sub_bytes = (size_t)kLanes * 128 + (size_t)bn * 128;
+    static const int kpb_env = getenv("EB_KPB") ? atoi(getenv("EB_KPB")) : 0;
+    p.kpb = kpb_env > 0 ? (kpb_env > 8 ? 8 : kpb_env) : (bn <= 32 ? 2 : 1);
+    const size_t stage_bytes = sub_bytes * p.kpb;
+    static const int budget_env = getenv("EB_SMEM_KB") ? atoi(getenv("EB_SMEM_KB")) : 0;
+    const size_t budget = (size_t)(budget_env > 0 ? budget_env : 200) * 1024;
+    const size_t fixed = kBarrierBytes + 1024;                      // barriers, alignment
+    int stages = (int)((budget - fixed) / stage_bytes);
+    stages = stages > kMaxStages ? kMaxStages : (stages < 2 ? 2 : stages);
+    p.stages = stages;
+    const size_t smem = fixed + (size_t)stages * stage_bytes;
+    swap_split(N, K, p.kpb, &grid, &p.units_per_cta);
     const size_t tiles = (N + kLanes - 1) / kLanes;
     EB_REQUIRE(tiles * sizeof(int) <= kCounterBytes, "gemm: N=%d exceeds the decode path's tile-counter capacity", N);
     // The counters sit at a fixed place (the head of the workspace) so that calls of any
@@ -622,13 +706,13 @@ extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ld
     p.lane_rows = N; p.col_rows = M;
     if ((rc = make_map(&tl, W, dtype, N, K, ldw, kLanes))) return rc;
     if ((rc = make_map(&tc, A, dtype, M, K, lda, bn))) return rc;
-#define EB_SWAP(BN, ST)                                                                            \
-  (dtype == EB_F16 ? launch<__half, BN, ST, true>(tl, tc, p, grid, st)                             \
-                   : launch<__nv_bfloat16, BN, ST, true>(tl, tc, p, grid, st))
-    if (bn == 16) return EB_SWAP(16, 10);
-    if (bn == 32) return EB_SWAP(32, 10);
-    if (bn == 64) return EB_SWAP(64, 8);
-    return EB_SWAP(128, 6);
+#define EB_SWAP(BN)                                                                             \
+  (dtype == EB_F16 ? launch<__half, BN, true>(tl, tc, p, grid, smem, st)                        \
+                   : launch<__nv_bfloat16, BN, true>(tl, tc, p, grid, smem, st))
+    if (bn == 16) return EB_SWAP(16);
+    if (bn == 32) return EB_SWAP(32);
+    if (bn == 64) return EB_SWAP(64);
+    return EB_SWAP(128);
 #undef EB_SWAP
   }
   p.lane_rows = M; p.col_rows = N;
@@ -637,11 +721,14 @@ extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ld
   const int bn = wide ? 256 : 128;
   const long long tiles = lane_tiles * ((N + bn - 1) / bn);
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  p.stages = wide ? 4 : 6;
+  p.kpb = 1;
+  const size_t smem = kBarrierBytes + 1024 + (size_t)p.stages * (kLanes * 128 + bn * 128);
   if ((rc = make_map(&tl, A, dtype, M, K, lda, kLanes))) return rc;
   if ((rc = make_map(&tc, W, dtype, N, K, ldw, bn))) return rc;
   if (bn == 256)
-    return dtype == EB_F16 ? launch<__half, 256, 4, false>(tl, tc, p, grid, st)
-                           : launch<__nv_bfloat16, 256, 4, false>(tl, tc, p, grid, st);
-  return dtype == EB_F16 ? launch<__half, 128, 6, false>(tl, tc, p, grid, st)
-                         : launch<__nv_bfloat16, 128, 6, false>(tl, tc, p, grid, st);
+    return dtype == EB_F16 ? launch<__half, 256, false>(tl, tc, p, grid, smem, st)
+                           : launch<__nv_bfloat16, 256, false>(tl, tc, p, grid, smem, st);
+  return dtype == EB_F16 ? launch<__half, 128, false>(tl, tc, p, grid, smem, st)
+                         : launch<__nv_bfloat16, 128, false>(tl, tc, p, grid, smem, st);
 }

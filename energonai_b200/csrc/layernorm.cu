@@ -25,6 +25,8 @@ ln_cached_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restri
   using PI = Pack<Tin, VEC>;
   using PO = Pack<Tout, VEC>;
   __shared__ float scratch[kThreads / 32];
+  griddep_wait();
+  griddep_launch();
   const int packs = n2 / VEC;
   const float inv_n = 1.f / (float)n2;
   for (long long row = blockIdx.x; row < n1; row += gridDim.x) {
@@ -105,6 +107,8 @@ ln_generic_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restr
                   Tin *__restrict__ sum_out, const Tout *__restrict__ gamma, const Tout *__restrict__ beta,
                   long long n1, int n2, float eps) {
   __shared__ float scratch[kThreads / 32];
+  griddep_wait();
+  griddep_launch();
   const float inv_n = 1.f / (float)n2;
   for (long long row = blockIdx.x; row < n1; row += gridDim.x) {
     const Tin *xr = x + row * n2;
@@ -157,13 +161,13 @@ int launch_ln(void *y, float *mean, float *invvar, const void *x, const void *re
                    (const Tout *)gamma, (const Tout *)beta, n1, n2, eps
   if (vec_ok && packs <= kThreads * 16) {
     const int need = (packs + kThreads - 1) / kThreads;
-    if (need <= 1) ln_cached_kernel<Tin, Tout, 1><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
-    else if (need <= 2) ln_cached_kernel<Tin, Tout, 2><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
-    else if (need <= 4) ln_cached_kernel<Tin, Tout, 4><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
-    else if (need <= 8) ln_cached_kernel<Tin, Tout, 8><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
-    else ln_cached_kernel<Tin, Tout, 16><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
+    if (need <= 1) launch_pdl(ln_cached_kernel<Tin, Tout, 1>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else if (need <= 2) launch_pdl(ln_cached_kernel<Tin, Tout, 2>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else if (need <= 4) launch_pdl(ln_cached_kernel<Tin, Tout, 4>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else if (need <= 8) launch_pdl(ln_cached_kernel<Tin, Tout, 8>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else launch_pdl(ln_cached_kernel<Tin, Tout, 16>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
   } else {
-    ln_generic_kernel<Tin, Tout><<<grid, kThreads, 0, st>>>(EB_LN_ARGS);
+    launch_pdl(ln_generic_kernel<Tin, Tout>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
   }
 #undef EB_LN_ARGS
   return check_launch("layer_norm_fwd");

@@ -9,8 +9,8 @@ _workspaces = {}
 
 
 def workspace(device, nbytes):
-    """Per-device scratch for the small-M (decode) GEMM: zero-filled once, grown on demand.
-    One buffer per device is enough because calls on a device are issued on one stream."""
+    """Per-device scratch for the small-M (generation-step) GEMM: zero-filled once, grown on
+    demand.  One buffer per device is enough because calls on a device are issued on one stream."""
     key = torch.device(device).index
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
@@ -20,12 +20,14 @@ def workspace(device, nbytes):
 
 
 def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out_rows_per_batch=0,
-         out_batch_stride=0, out_ld=None, out_row_offset_device=None):
+         out_batch_stride=0, out_ld=None, out_row_offset_device=None, static_weight=False):
     """a [M,K] (row stride allowed), w [N,K]; returns out [M,N].
 
     `out`, if given, receives the result; with out_rows_per_batch > 0 row m is written at
     element (m // rpb) * out_batch_stride + (m % rpb) * out_ld of `out` (a view into a cache);
-    out_row_offset_device (int32 device scalar) adds that many rows of out_ld at run time."""
+    out_row_offset_device (int32 device scalar) adds that many rows of out_ld at run time.
+    static_weight=True promises that `w` is not being written by earlier work still in flight
+    on the stream (model weights), which lets the kernel prefetch it early."""
     require_cuda(a, w, bias, residual, out)
     if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1]:
         raise RuntimeError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T do not match")
@@ -50,7 +52,7 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
     check(lib().eb_gemm(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out_ld, ptr(bias), ptr(residual),
                         residual.stride(0) if residual is not None else 0, M, N, K, dtype_code(a.dtype),
                         dtype_code(out_dtype), code, out_rows_per_batch, out_batch_stride,
-                        ptr(out_row_offset_device), ptr(ws),
+                        ptr(out_row_offset_device), 1 if static_weight else 0, ptr(ws),
                         ws.numel() if ws is not None else 0, stream_ptr()), "gemm")
     return out
 

@@ -111,7 +111,7 @@ class MultiHeadAttention1D(nn.Module):
                 cache.reset()
                 cache.ensure(B, S, 3 * hl, x.dtype, x.device)
                 buf = cache.buf
-            gemm(x, w, bias=b, out=buf, out_rows_per_batch=S, out_batch_stride=buf.stride(0), out_ld=buf.stride(1))
+            gemm(x, w, bias=b, static_weight=True, out=buf, out_rows_per_batch=S, out_batch_stride=buf.stride(0), out_ld=buf.stride(1))
             kv_len = S
             mask = attention_mask.reshape(B, -1) if attention_mask is not None else None
             ctx = attention_prefill(buf[:, :S, 2 * hl:], buf[:, :S, :hl], buf[:, :S, hl:2 * hl], d, mask=mask,
@@ -126,7 +126,7 @@ class MultiHeadAttention1D(nn.Module):
                 pos = cache.len
                 cache.ensure(B, pos + 1, 3 * hl, x.dtype, x.device)
                 buf = cache.buf
-                gemm(x, w, bias=b, out=buf[:, pos:], out_rows_per_batch=1, out_batch_stride=buf.stride(0),
+                gemm(x, w, bias=b, static_weight=True, out=buf[:, pos:], out_rows_per_batch=1, out_batch_stride=buf.stride(0),
                      out_ld=buf.stride(1))
                 cache.len = kv_len = pos + 1
                 ctx = attention_decode(buf[:, :, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, kv_len, mask=mask,
@@ -134,7 +134,7 @@ class MultiHeadAttention1D(nn.Module):
             else:
                 buf = cache.buf
                 cap = buf.shape[1]
-                gemm(x, w, bias=b, out=buf, out_rows_per_batch=1, out_batch_stride=buf.stride(0), out_ld=buf.stride(1),
+                gemm(x, w, bias=b, static_weight=True, out=buf, out_rows_per_batch=1, out_batch_stride=buf.stride(0), out_ld=buf.stride(1),
                      out_row_offset_device=kv_state[0:1])
                 ctx = attention_decode(buf[:, :, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, cap, mask=mask,
                                        scale=self.scaling, q_in_cache=True, kv_len_device=kv_state[1:2])

@@ -15,7 +15,7 @@ class _Classifier(nn.Module):
         self.bias = nn.Parameter(torch.zeros(num_classes, dtype=dtype)) if bias else None
 
     def forward(self, x):
-        y = gemm(x.reshape(-1, x.shape[-1]), self.weight, bias=self.bias, out_dtype=torch.float32)
+        y = gemm(x.reshape(-1, x.shape[-1]), self.weight, bias=self.bias, out_dtype=torch.float32, static_weight=True)
         return y.view(*x.shape[:-1], self.weight.shape[0])
 
 

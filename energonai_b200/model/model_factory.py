@@ -79,7 +79,7 @@ class PipelineModel(nn.Module):
             hidden = block(hidden_states=hidden, attention_mask=st["mask4"], first_cache=False, kv_state=st["kv_state"])
         logits = self.head(self.norm(hidden))[:, -1, :]
         tok = logits.argmax(-1)
-        st["out_ids"].index_copy_(1, pos_long, tok.view(-1, 1))
+        st["out_ids"].index_copy_(1, st["kv_state"][1:2].to(torch.long), tok.view(-1, 1))   # the new token's index
         st["tok"].copy_(tok)
         st["kv_state"].add_(1)
 

@@ -33,7 +33,7 @@ class Linear1D_Col(nn.Module):
         nn.init.normal_(self.weight, std=0.02)
 
     def forward(self, x, act=None):
-        y = gemm(_flat(x), self.weight, bias=self.bias, act=act).view(*x.shape[:-1], self.out_per_rank)
+        y = gemm(_flat(x), self.weight, bias=self.bias, act=act, static_weight=True).view(*x.shape[:-1], self.out_per_rank)
         return get_tp().all_gather_last_dim(y) if self.gather_output else y
 
 
@@ -54,7 +54,7 @@ class Linear1D_Row(nn.Module):
         tp = get_tp()
         lead = tp.rank == 0
         res = _flat(residual) if (residual is not None and lead) else None
-        y = gemm(_flat(x), self.weight, bias=self.bias if lead else None, residual=res)
+        y = gemm(_flat(x), self.weight, bias=self.bias if lead else None, residual=res, static_weight=True)
         tp.all_reduce(y)
         return y.view(*x.shape[:-1], self.out_features)
 

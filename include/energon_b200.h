@@ -47,6 +47,10 @@ extern "C" {
 #define EB_ACT_GELU_TANH 2 /* energonai/model/model_factory.py:32-35 (gelu_impl)            */
 #define EB_ACT_GELU_ERF 3  /* torch.nn.functional.gelu                                      */
 
+/* flags for eb_gemm */
+#define EB_GEMM_STATIC_W 1 /* W is constant (model weights): the kernel may start reading it while
+                              earlier work of the stream is still running */
+
 /* flags for eb_scale_mask_softmax */
 #define EB_SM_CAUSAL 1  /* keys j > query i are masked to exactly 0 (reference behaviour)    */
 #define EB_SM_KEYLEN 2  /* keys j >= real_seq_len[b] are masked to exactly 0                 */
@@ -150,14 +154,19 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
  *   at a position that advances between replays.
  *   K, N, all leading dimensions and c_batch_stride must be multiples of 8, pointers 16-byte
  *   aligned.
- * For M <= 128 (decode) the kernel streams W once, split evenly over all SMs, and combines
- * partial sums through `workspace`: at least eb_gemm_workspace_bytes(M,N,K) bytes, 16-byte
- * aligned, zero-filled once before first use (the kernel leaves it reusable).  Calls that
- * share a workspace must not overlap on the device.  workspace may be NULL for M > 128. */
+ * The kernel is launched so that it may begin before the preceding kernel of the stream has
+ * finished; it reads A, bias and residual only after that kernel completed, and W too unless
+ * flags has EB_GEMM_STATIC_W.
+ * For M <= 128 (generation steps) the kernel streams W exactly once, split evenly over all SMs
+ * (stream-K over 128-row tiles), and combines the partial sums of tiles shared by several CTAs
+ * through `workspace`: at least eb_gemm_workspace_bytes(M,N,K) bytes, 16-byte aligned,
+ * zero-filled once before first use (the kernel leaves it reusable; summation order is fixed,
+ * results are deterministic).  Calls that share a workspace must not overlap on the device.
+ * workspace may be NULL for M > 128. */
 EB_API int eb_gemm(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc, const void *bias,
             const void *residual, long long ldr, int M, int N, int K, int dtype, int out_dtype, int act,
-            int c_rows_per_batch, long long c_batch_stride, const int32_t *c_row_offset_device, void *workspace,
-            size_t workspace_bytes, void *stream);
+            int c_rows_per_batch, long long c_batch_stride, const int32_t *c_row_offset_device, int flags,
+            void *workspace, size_t workspace_bytes, void *stream);
 EB_API size_t eb_gemm_workspace_bytes(int M, int N, int K);
 
 /* ---- fused attention ----------------------------------------------------------------------- */
