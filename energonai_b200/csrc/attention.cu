@@ -541,3 +541,58 @@ extern "C" int eb_attention_decode(const void *q, const void *k, const void *v, 
   if (dtype == EB_F16) return head_dim == 64 ? launch_decode<__half, 64>(p, st) : launch_decode<__half, 128>(p, st);
   return head_dim == 64 ? launch_decode<__nv_bfloat16, 64>(p, st) : launch_decode<__nv_bfloat16, 128>(p, st);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Generation-step attention for callers that must not allocate device memory
+// ------------------------------------------------------------------------------------------------
+// Some hosts of this library cannot call cudaMalloc on the serving path: a worker whose memory
+// pool was sized and handed out once at start-up, code running inside a region where the
+// allocator is locked, or an embedding that is only given raw pointers to tensors somebody
+// else owns.  For them the split-KV scratch lives in the library image itself: a fixed array
+// in device memory that every GPU loading the library carries until the process exits.
+constexpr size_t kStaticScratchBytes = 8u << 20;   // 64 KB of counters + ~7.9 MB of partial results
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticScratchBytes];
+
+extern "C" int eb_attention_decode_noalloc(const void *q, const void *k, const void *v, void *out, const void *mask,
+                                           long long q_batch_stride, long long q_row_stride,
+                                           long long k_batch_stride, long long k_row_stride,
+                                           long long v_batch_stride, long long v_row_stride,
+                                           long long o_batch_stride, long long mask_batch_stride, int batch,
+                                           int heads, int kv_len, const int32_t *kv_len_device, int head_dim,
+                                           float scale, int dtype, int nsplit, void *stream) {
+  // In host code the array's name is only a handle for the runtime, not a device address; the
+  // address is looked up once per device, with that device current, and remembered.
+  static void *device_ptr[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return fail(EB_ECUDA, "attention_decode_noalloc: no usable current device");
+  }
+  const size_t need = eb_attention_decode_scratch_bytes(batch, heads, head_dim, nsplit);
+  if (need > kStaticScratchBytes)
+    return fail(EB_ELIMIT,
+                "attention_decode_noalloc: batch %d x heads %d x nsplit %d needs %zu bytes of scratch, the built-in "
+                "array holds %zu; lower nsplit or use eb_attention_decode with a caller-provided scratch",
+                batch, heads, nsplit, need, (size_t)kStaticScratchBytes);
+  if (device_ptr[dev] == nullptr) {
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_decode_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return fail(EB_ECUDA, "attention_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    }
+    // The arrival counters at the head of the array must start at zero.  A freshly loaded image
+    // is zero already; clearing them here also covers a process that reuses the device after an
+    // aborted call.  (Stream-ordered, so this first call should not be inside a stream capture.)
+    e = cudaMemsetAsync(ptr, 0, 64 * 1024, as_stream(stream));
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(EB_ECUDA, "attention_decode_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
+    }
+    device_ptr[dev] = ptr;
+  }
+  return eb_attention_decode(q, k, v, out, mask, q_batch_stride, q_row_stride, k_batch_stride, k_row_stride,
+                             v_batch_stride, v_row_stride, o_batch_stride, mask_batch_stride, batch, heads, kv_len,
+                             kv_len_device, head_dim, scale, dtype, nsplit, device_ptr[dev], kStaticScratchBytes,
+                             stream);
+}

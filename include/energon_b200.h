@@ -205,6 +205,24 @@ EB_API int eb_attention_decode(const void *q, const void *k, const void *v, void
                         void *stream);
 EB_API size_t eb_attention_decode_scratch_bytes(int batch, int heads, int head_dim, int nsplit);
 
+/* The same computation as eb_attention_decode for callers that cannot allocate device memory
+ * (a serving worker whose pool was carved up at start-up, code running while the allocator is
+ * locked, a host that only receives raw pointers): the split-KV scratch is an 8 MiB array built
+ * into the library, resident on every GPU that loads it until the process exits.  The caller
+ * passes inputs and outputs only.  Requests whose scratch (see
+ * eb_attention_decode_scratch_bytes) exceeds 8 MiB are refused with EB_ELIMIT.  The first call on
+ * each device looks the array's address up and clears its counters on `stream`; make that
+ * first call outside any stream capture.  All calls on a device share the one array and it
+ * keeps the previous call's contents, so calls that overlap on the GPU (two streams, two
+ * threads) race: serialise them.  Nothing is allocated or freed.  No counterpart in the
+ * reference. */
+EB_API int eb_attention_decode_noalloc(const void *q, const void *k, const void *v, void *out, const void *mask,
+                                long long q_batch_stride, long long q_row_stride, long long k_batch_stride,
+                                long long k_row_stride, long long v_batch_stride, long long v_row_stride,
+                                long long o_batch_stride, long long mask_batch_stride, int batch, int heads,
+                                int kv_len, const int32_t *kv_len_device, int head_dim, float scale, int dtype,
+                                int nsplit, void *stream);
+
 /* Device-side waits are bounded; when one expires the kernel records it and returns.  This
  * reads (synchronously) the status word of the current device: out4[0] = 0 or EB_ETIMEDOUT,
  * out4[1] = which wait, out4[2] = block, out4[3] = detail.  clear != 0 resets it.  No
