@@ -294,9 +294,19 @@ def run_ours(args):
                 "traffic": 162.0e6 if (world == 1 and not args.layers) else None, "kernel": "gemm_kernel<__half, 16, true> (generation-step GEMM, M = batch 16)",
                 "peak_kind": f"of {peak_kind}", "launches_timed": gemm_n,
                 "algorithmic_bytes_per_launch": gemm_bytes / max(1, gemm_n), "us_per_launch": gemm_ms * 1e3 / max(1, gemm_n)}
-    if rank != 0:
+    def finish():
+        # Captured graphs hold NCCL kernels; tearing the process group down under them can
+        # block, so release the graphs, rendezvous once more and leave without the teardown.
         if world > 1:
-            dist.destroy_process_group()
+            model._decode_state = None
+            torch.cuda.synchronize()
+            dist.barrier()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
+    if rank != 0:
+        finish()
         return
     ms_per_step = elapsed_ms / args.steps
     value = tokens_per_step / (ms_per_step * 1e-3)
@@ -317,11 +327,13 @@ def run_ours(args):
     if args.layers or args.new_tokens:
         line["config"]["reduced"] = f"depth {cfg['depth']}, new_tokens {cfg['new_tokens']} (debug run, not the named config)"
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    finish()
 
 
 def main():
+    if os.environ.get("EB_BENCH_WATCHDOG"):       # debugging aid: dump all Python stacks if the run stalls
+        import faulthandler
+        faulthandler.dump_traceback_later(int(os.environ["EB_BENCH_WATCHDOG"]), repeat=False, exit=True)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
