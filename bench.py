@@ -215,7 +215,10 @@ def run_ours(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        tp.init_tp(world)
+        ctx = tp.init_tp(world)
+        if os.environ.get("EB_PEER", "1") != "0":
+            # generation steps: all-reduce fused into the row-parallel GEMM epilogue (NVLink peer stores)
+            ctx.enable_peer_exchange(CFG["batch"], CFG["hidden"])
     cfg = dict(CFG)
     if args.layers:
         cfg["depth"] = args.layers

@@ -49,6 +49,17 @@ constexpr uint32_t kBarrierBytes = 1024;      // head of shared memory: mbarrier
 
 __device__ int g_status[4];      // [0] code (0 = ok), [1] where, [2] block, [3] detail
 
+// Peer exchange of the fused row-parallel GEMM + all-reduce (generation orientation only).
+// Every rank owns a receive area [2 parities][world sources][M][N] fp32 and a flag area
+// [2][world][tiles] u32 in memory its peers can address over NVLink.
+struct CommParams {
+  int rank, world;               // world <= 1: no exchange
+  int parity;                    // alternates between consecutive calls (double buffering)
+  float *recv[8];                // recv[r]: base of rank r's receive area (recv[rank] is local)
+  uint32_t *flags[8];            // flags[r]: base of rank r's flag area
+  int max_tiles;                 // flag slots per (parity, source)
+};
+
 struct GemmParams {
   int M, N, K;                   // logical problem: C[M,N] = A[M,K] W[N,K]^T
   int lane_rows, col_rows;       // rows of the lane-side / column-side operand (swap: N, M)
@@ -69,6 +80,7 @@ struct GemmParams {
   int stages;                    // pipeline depth actually used (<= kMaxStages)
   int kpb;                       // k-blocks (64 columns each) per pipeline stage / barrier hand-over
   int static_w;                  // W may be read before the preceding kernel of the stream has finished
+  CommParams comm;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -151,6 +163,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float *p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
 }
 
 // Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
@@ -522,6 +548,59 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
             }
           }
         }
+        if (do_epilogue && p.comm.world > 1) {
+          // Fused all-reduce: this CTA holds the rank's complete partial product of the tile.
+          // Push it into every rank's receive area (plain stores over NVLink), publish a flag
+          // per destination, wait (bounded) for the flags of all sources in the local area,
+          // then sum the sources in rank order, identically on every rank.
+          const CommParams &cm = p.comm;
+          const size_t slot = (size_t)p.M * p.N;                        // floats per (parity, source)
+          const size_t my_off = ((size_t)cm.parity * cm.world + cm.rank) * slot;
+          if (n_ok) {
+            for (int r = 0; r < cm.world; ++r) {
+              float *dst = cm.recv[r] + my_off + n;
+#pragma unroll
+              for (int m = 0; m < BN; ++m)
+                if (m < p.M) dst[(size_t)m * p.N] = v[m];
+            }
+          }
+          __threadfence_system();
+          if (!epi_sync()) { alive = false; continue; }
+          const int et = threadIdx.x - 64;                              // 0..127 among the epilogue threads
+          const size_t flag_idx = ((size_t)cm.parity * cm.world) * cm.max_tiles + s.lane_tile;
+          if (et < cm.world) st_release_sys(cm.flags[et] + flag_idx + (size_t)cm.rank * cm.max_tiles, 1u);
+          if (et < cm.world) {
+            uint32_t *mine = cm.flags[cm.rank] + flag_idx + (size_t)et * cm.max_tiles;
+            const unsigned long long t0 = globaltimer();
+            bool got = false;
+            for (unsigned it = 1; !got; ++it) {
+              got = ld_acquire_sys(mine) != 0u;
+              if (!got && (it & 63u) == 0) {
+                if (*abort_flag) break;
+                if (globaltimer() - t0 > kWaitBudgetNs) {
+                  *abort_flag = 1;
+                  if (atomicCAS(&g_status[0], 0, EB_ETIMEDOUT) == 0) {
+                    g_status[1] = 6; g_status[2] = blockIdx.x; g_status[3] = et;
+                  }
+                  break;
+                }
+              }
+            }
+            if (got) *mine = 0u;                                        // consumed: ready for the next use of this slot
+          }
+          if (!epi_sync()) { alive = false; continue; }
+          if (*abort_flag) { alive = false; continue; }
+          if (n_ok) {
+            const float *src = cm.recv[cm.rank] + (size_t)cm.parity * cm.world * slot + n;
+#pragma unroll
+            for (int m = 0; m < BN; ++m) v[m] = 0.f;
+            for (int r = 0; r < cm.world; ++r) {
+#pragma unroll
+              for (int m = 0; m < BN; ++m)
+                if (m < p.M) v[m] += ld_relaxed_sys_f32(src + (size_t)r * slot + (size_t)m * p.N);
+            }
+          }
+        }
         if (do_epilogue && n_ok) {
           const float b = bias ? to_f32<T>(bias[n]) : 0.f;
 #pragma unroll
@@ -647,11 +726,11 @@ extern "C" int eb_device_status(int *out4, int clear) {
   return EB_OK;
 }
 
-extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
-                       const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
-                       int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
-                       const int32_t *c_row_offset_device, int flags, void *workspace, size_t workspace_bytes,
-                       void *stream) {
+static int gemm_impl(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
+                     const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
+                     int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
+                     const int32_t *c_row_offset_device, int flags, void *workspace, size_t workspace_bytes,
+                     void *stream, const CommParams *comm) {
   EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "gemm: operands must be fp16 or bf16 (got dtype %d)", dtype);
   EB_REQUIRE(out_dtype == dtype || out_dtype == EB_F32, "gemm: output must be the input type or fp32");
   EB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative size");
@@ -673,6 +752,10 @@ extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ld
   p.C = C; p.ldc = ldc; p.c_rows_per_batch = c_rows_per_batch; p.c_batch_stride = c_batch_stride;
   p.c_row_offset_dev = c_row_offset_device;
   p.static_w = (flags & EB_GEMM_STATIC_W) ? 1 : 0;
+  if (comm) p.comm = *comm;
+  EB_REQUIRE(!comm || comm->world <= 1 || M <= kLanes, "gemm_allreduce: the fused exchange serves M <= 128 only (M=%d)", M);
+  EB_REQUIRE(!comm || comm->world <= 1 || (long long)((N + kLanes - 1) / kLanes) <= comm->max_tiles,
+             "gemm_allreduce: N=%d needs more flag slots than the exchange area has", N);
   p.bias = bias; p.residual = residual; p.ldr = ldr; p.act = act; p.out_f32 = out_dtype == EB_F32 && dtype != EB_F32;
 
   CUtensorMap tl, tc;
@@ -731,4 +814,42 @@ extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ld
                            : launch<__nv_bfloat16, 256, false>(tl, tc, p, grid, smem, st);
   return dtype == EB_F16 ? launch<__half, 128, false>(tl, tc, p, grid, smem, st)
                          : launch<__nv_bfloat16, 128, false>(tl, tc, p, grid, smem, st);
+}
+
+extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
+                       const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
+                       int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
+                       const int32_t *c_row_offset_device, int flags, void *workspace, size_t workspace_bytes,
+                       void *stream) {
+  return gemm_impl(A, lda, W, ldw, C, ldc, bias, residual, ldr, M, N, K, dtype, out_dtype, act, c_rows_per_batch,
+                   c_batch_stride, c_row_offset_device, flags, workspace, workspace_bytes, stream, nullptr);
+}
+
+extern "C" size_t eb_gemm_allreduce_recv_bytes(int world, int M, int N) {
+  return (size_t)2 * world * M * N * sizeof(float);
+}
+
+extern "C" int eb_gemm_allreduce(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
+                                 const void *bias, const void *residual, long long ldr, int M, int N, int K,
+                                 int dtype, int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
+                                 const int32_t *c_row_offset_device, int flags, void *workspace,
+                                 size_t workspace_bytes, int rank, int world, void *const *peer_recv,
+                                 void *const *peer_flags, size_t recv_bytes, int flag_slots_per_source, int parity,
+                                 void *stream) {
+  EB_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world, "gemm_allreduce: bad rank %d / world %d", rank, world);
+  EB_REQUIRE(parity == 0 || parity == 1, "gemm_allreduce: parity must be 0 or 1");
+  CommParams cm{};
+  cm.rank = rank; cm.world = world; cm.parity = parity; cm.max_tiles = flag_slots_per_source;
+  if (world > 1) {
+    EB_REQUIRE(peer_recv && peer_flags && flag_slots_per_source > 0, "gemm_allreduce: missing exchange areas");
+    EB_REQUIRE(recv_bytes >= eb_gemm_allreduce_recv_bytes(world, M, N),
+               "gemm_allreduce: receive areas of %zu bytes are too small for world %d, M %d, N %d", recv_bytes, world, M, N);
+    for (int r = 0; r < world; ++r) {
+      EB_REQUIRE(peer_recv[r] && peer_flags[r], "gemm_allreduce: null exchange area for rank %d", r);
+      cm.recv[r] = reinterpret_cast<float *>(peer_recv[r]);
+      cm.flags[r] = reinterpret_cast<uint32_t *>(peer_flags[r]);
+    }
+  }
+  return gemm_impl(A, lda, W, ldw, C, ldc, bias, residual, ldr, M, N, K, dtype, out_dtype, act, c_rows_per_batch,
+                   c_batch_stride, c_row_offset_device, flags, workspace, workspace_bytes, stream, &cm);
 }

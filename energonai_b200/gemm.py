@@ -20,7 +20,7 @@ def workspace(device, nbytes):
 
 
 def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out_rows_per_batch=0,
-         out_batch_stride=0, out_ld=None, out_row_offset_device=None, static_weight=False):
+         out_batch_stride=0, out_ld=None, out_row_offset_device=None, static_weight=False, peer=None):
     """a [M,K] (row stride allowed), w [N,K]; returns out [M,N].
 
     `out`, if given, receives the result; with out_rows_per_batch > 0 row m is written at
@@ -49,6 +49,17 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
     code = ACT_CODES[act] if not isinstance(act, int) else act
     nbytes = lib().eb_gemm_workspace_bytes(M, N, K)
     ws = workspace(a.device, nbytes) if nbytes else None
+    if peer is not None and peer.world > 1:
+        if not peer.fits(M, N):
+            raise RuntimeError(f"gemm: {M} x {N} does not fit the peer exchange areas")
+        check(lib().eb_gemm_allreduce(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out_ld, ptr(bias), ptr(residual),
+                                      residual.stride(0) if residual is not None else 0, M, N, K, dtype_code(a.dtype),
+                                      dtype_code(out_dtype), code, out_rows_per_batch, out_batch_stride,
+                                      ptr(out_row_offset_device), 1 if static_weight else 0, ptr(ws),
+                                      ws.numel() if ws is not None else 0, peer.rank, peer.world, peer.recv_ptrs,
+                                      peer.flag_ptrs, peer.recv_bytes, 1024, peer.next_parity(), stream_ptr()),
+              "gemm_allreduce")
+        return out
     check(lib().eb_gemm(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out_ld, ptr(bias), ptr(residual),
                         residual.stride(0) if residual is not None else 0, M, N, K, dtype_code(a.dtype),
                         dtype_code(out_dtype), code, out_rows_per_batch, out_batch_stride,

@@ -52,6 +52,12 @@ class Linear1D_Row(nn.Module):
         the sum exactly once: rank 0 adds them in its GEMM epilogue, then the partial products
         are all-reduced."""
         tp = get_tp()
+        x2 = _flat(x)
+        if tp.peer is not None and tp.peer.fits(x2.shape[0], self.out_features):
+            # generation steps: the all-reduce runs inside the GEMM epilogue over NVLink peer stores
+            res = _flat(residual) if residual is not None else None
+            y = gemm(x2, self.weight, bias=self.bias, residual=res, static_weight=True, peer=tp.peer)
+            return y.view(*x.shape[:-1], self.out_features)
         lead = tp.rank == 0
         res = _flat(residual) if (residual is not None and lead) else None
         y = gemm(_flat(x), self.weight, bias=self.bias if lead else None, residual=res, static_weight=True)

@@ -13,6 +13,16 @@ import torch.distributed as dist
 class TPContext:
     def __init__(self, group=None, rank=0, world_size=1):
         self.group, self.rank, self.world_size = group, rank, world_size
+        self.peer = None       # PeerExchange for the fused GEMM + all-reduce (enable_peer_exchange)
+
+    def enable_peer_exchange(self, max_rows, max_cols):
+        """Allocates and maps the NVLink exchange areas (collective over the group).  Row-parallel
+        layers then fuse the all-reduce into the GEMM epilogue for up to max_rows x max_cols
+        outputs (rows <= 128); larger products keep using NCCL."""
+        if self.world_size > 1 and self.peer is None:
+            from .comm import PeerExchange
+            self.peer = PeerExchange(self.group, self.rank, self.world_size, max_rows, max_cols)
+        return self.peer
 
     def all_reduce(self, t):
         """In-place SUM over the tensor-parallel group (no-op for one rank)."""

@@ -169,6 +169,28 @@ EB_API int eb_gemm(const void *A, long long lda, const void *W, long long ldw, v
             void *workspace, size_t workspace_bytes, void *stream);
 EB_API size_t eb_gemm_workspace_bytes(int M, int N, int K);
 
+/* Row-parallel GEMM with the tensor-parallel all-reduce fused into its epilogue, for the
+ * generation orientation (M <= 128).  Replaces "F.linear, then dist.all_reduce, then + bias" of
+ * colossalai's Linear1D_Row (the row-parallel layers constructed at
+ * energonai/model/attention.py:37 and energonai/model/mlp.py:22).  Arguments as eb_gemm, plus the
+ * exchange areas: every rank owns a receive area of eb_gemm_allreduce_recv_bytes(world, M, N)
+ * bytes (or more) and a flag area of 2*world*flag_slots_per_source uint32 (zero before first
+ * use), both addressable by its peers (NVLink peer mapping); peer_recv[r] / peer_flags[r] are
+ * HOST arrays of `world` device pointers to rank r's areas as mapped in this process.  The CTA
+ * that completes a tile stores its fp32 partial into every rank's receive area with plain peer
+ * stores, publishes one flag per destination, waits (bounded, 1 s, see eb_device_status) for all
+ * sources' flags in its own area, and sums the sources in rank order, so every rank obtains the
+ * bit-identical result; bias, activation and residual are applied after the sum on every rank.
+ * `parity` must alternate (0,1,0,1,...) over the successive calls that share the areas, in the
+ * same order on all ranks.  world == 1 degenerates to eb_gemm. */
+EB_API int eb_gemm_allreduce(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
+                      const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
+                      int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
+                      const int32_t *c_row_offset_device, int flags, void *workspace, size_t workspace_bytes,
+                      int rank, int world, void *const *peer_recv, void *const *peer_flags, size_t recv_bytes,
+                      int flag_slots_per_source, int parity, void *stream);
+EB_API size_t eb_gemm_allreduce_recv_bytes(int world, int M, int N);
+
 /* ---- fused attention ----------------------------------------------------------------------- */
 
 /* Replaces the score / mask / softmax / value products of MultiHeadAttention1D.forward

@@ -15,7 +15,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, ret, use_peer=False):
     import torch.distributed as dist
     from oracle import inputs, layers
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
@@ -25,8 +25,11 @@ def _worker(rank, world, port, ret):
         from energonai_b200 import tp
         from energonai_b200.model import Block1D
         from energonai_b200.sharding import shard_block_state
-        tp.init_tp(world)
+        ctx = tp.init_tp(world)
         h, H, f, B, S = 512, 8, 2048, 3, 40
+        if use_peer:
+            ctx.enable_peer_exchange(16, 5120)
+            assert ctx.peer is not None
         gen = torch.Generator().manual_seed(9)
         bp = inputs.block_params(gen, h, f, rich=True, std=0.04)
         x = torch.randn(B, S + 2, h, generator=gen)
@@ -47,15 +50,36 @@ def _worker(rank, world, port, ret):
                     exp = ref(x[:, :cur], m4, step == 0)
                     a, b = (out[m.bool()], exp[m.bool()]) if step == 0 else (out[:, -1], exp[:, -1])
                     ok = ok and bool(((a - b).abs() <= 2e-2 + 1e-2 * b.abs()).all())
+        if use_peer:
+            # the fused exchange against NCCL on the same operands: every rank gets the same bits
+            from energonai_b200.gemm import gemm, device_status
+            g = torch.Generator(device="cuda").manual_seed(100 + rank)
+            for M, N, K in ((16, 512, 1024), (3, 2048, 256), (16, 5120, 640)):
+                a = torch.randn(M, K, device="cuda", generator=g).half()
+                w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).half()
+                bias = torch.randn(N, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7)).half()
+                for _ in range(3):                                    # consecutive calls alternate the buffers
+                    fused = gemm(a, w, bias=bias, peer=ctx.peer)
+                part = (a.float() @ w.float().t())
+                dist.all_reduce(part)
+                exp = part + bias.float()
+                ok = ok and bool(((fused.float() - exp).abs() <= 2e-3 * exp.abs() + 2e-3 * exp.abs().max()).all())
+                gathered = [torch.empty_like(fused) for _ in range(world)]
+                dist.all_gather(gathered, fused)
+                ok = ok and all(torch.equal(gathered[0], t) for t in gathered)
+            ok = ok and device_status()[0] == 0
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_block_matches_oracle():
+@pytest.mark.parametrize("use_peer", [False, True])
+def test_two_gpu_block_matches_oracle(use_peer):
+    """use_peer=False: NCCL all-reduce after each row-parallel GEMM; use_peer=True: generation
+    steps run the all-reduce inside the GEMM epilogue over NVLink peer stores."""
     import torch.multiprocessing as mp
     world, port = 2, _free_port()
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, ret, use_peer), nprocs=world, join=True)
     assert all(ret.get(r) for r in range(world)), dict(ret)
