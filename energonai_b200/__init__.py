@@ -5,3 +5,17 @@ modules of `energonai.model`.  All compute runs in hand-written CUDA behind the 
 declared in include/energon_b200.h; there is no CPU or PyTorch fallback.
 """
 __version__ = "0.1.0"
+
+from .batch_mgr import BatchManager, SubmitEntry
+from .task import TaskEntry
+
+
+def __getattr__(name):
+    # launch_engine and QueueFullError pull in torch.distributed.rpc; import them on first use
+    if name in ("launch_engine", "QueueFullError", "AsyncEngine"):
+        from . import engine
+        return getattr(engine, name)
+    raise AttributeError(name)
+
+
+__all__ = ["BatchManager", "launch_engine", "SubmitEntry", "TaskEntry", "QueueFullError"]

@@ -1,0 +1,25 @@
+"""launch_engine / AsyncEngine / Worker over torch RPC with CPU (gloo) workers, mirroring the
+reference's engine tests (tests/test_engine/test_single_device.py, test_tp.py): BoringModel maps
+x to 4x + 1 for any tensor-parallel size; results come back by request id.  Each life cycle runs
+in its own process (energonai_b200/testing/engine_check.py)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("tp_world_size", [1, 2])
+def test_engine_life_cycle(tp_world_size):
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "energonai_b200.testing.engine_check", str(tp_world_size)], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0 and f"engine ok {tp_world_size}" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_pipeline_parallelism_is_rejected():
+    from energonai_b200.engine import AsyncEngine
+    with pytest.raises(RuntimeError, match="pp_world_size"):
+        AsyncEngine(1, 2, "127.0.0.1", 1, 1)
