@@ -44,11 +44,12 @@ def attention_prefill(q, k, v, head_dim, mask=None, causal=True, scale=None, out
 
 
 def pick_nsplit(batch, heads, kv_len, sm_count=148):
-    """Split the key range so that the grid is at least four waves of the three CTAs an SM
-    holds (short tails), without going below two 64-key tiles per CTA."""
+    """The fewest key splits that still give every SM its three resident CTAs (splitting costs a
+    merge and shortens the per-CTA stream: measured 35.5 / 38.6 / 40.7 us for 1 / 2 / 3 splits at
+    batch 16 x 40 heads x 576 keys), never more than one split per 64-key tile."""
     tiles = max(1, (kv_len + 63) // 64)
-    want = -(-4 * 3 * sm_count // max(1, batch * heads))
-    return max(1, min(want, max(1, tiles // 2), 64))
+    want = -(-3 * sm_count // max(1, batch * heads))
+    return max(1, min(want, tiles, 64))
 
 
 def attention_decode(q, k, v, head_dim, kv_len, mask=None, scale=None, out=None, nsplit=None, kv_len_device=None,

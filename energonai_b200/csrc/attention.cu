@@ -22,6 +22,7 @@ namespace {
 
 constexpr int kBM = 64, kBN = 64, kThreads = 128;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kDecodeStages = 2;   // key/value tiles in flight per CTA of the generation-step kernel
 
 struct AttnParams {
   const void *q, *k, *v;
@@ -86,16 +87,25 @@ template <int D> __device__ __forceinline__ uint32_t tile_off(int row, int chunk
 }
 
 // Load `kBN` rows starting at `row0` of a [*, D] slice (row stride rs elements) into a tile;
-// rows >= row_end are zero-filled.
+// rows >= row_end are zero-filled.  Thread t always moves 16-byte chunk (t % (D/8)) of rows
+// t / (D/8) + k * (kThreads / (D/8)); the row step is a multiple of 8, so the swizzle term is the
+// same for all of a thread's chunks and both addresses advance by constants.
 template <typename T, int D>
 __device__ __forceinline__ void load_tile(uint32_t tile, const T *base, long long rs, int row0, int row_end) {
-  constexpr int kChunks = D / 8;
+  constexpr int kChunks = D / 8, kRowStep = kThreads / kChunks, kIters = kBN / kRowStep;
+  static_assert(kRowStep % 8 == 0 && kBN % kRowStep == 0, "tile shape must keep the swizzle term constant per thread");
+  const int r0 = threadIdx.x / kChunks, c = threadIdx.x % kChunks;
+  uint32_t dst = tile + tile_off<D>(r0, c);
+  const T *src = base + (long long)(row0 + r0) * rs + c * 8;
+  const long long src_step = (long long)kRowStep * rs;
+  int row = row0 + r0;
 #pragma unroll
-  for (int i = threadIdx.x; i < kBN * kChunks; i += kThreads) {
-    const int r = i / kChunks, c = i % kChunks;
-    const bool ok = row0 + r < row_end;
-    const T *src = base + (long long)(ok ? row0 + r : row0) * rs + c * 8;
-    cp_async16(tile + tile_off<D>(r, c), src, ok);
+  for (int k = 0; k < kIters; ++k) {
+    const bool ok = row < row_end;
+    cp_async16(dst, ok ? src : base, ok);
+    dst += kRowStep * D * 2;
+    src += src_step;
+    row += kRowStep;
   }
 }
 
@@ -268,9 +278,12 @@ __global__ void __launch_bounds__(kThreads)
 attention_decode_kernel(const AttnParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kTileBytes = kBN * D * 2;
-  const uint32_t k_s = smem_u32(smem), v_s = k_s + 2 * kTileBytes;
-  float *mask_s = reinterpret_cast<float *>(smem + 4 * kTileBytes);            // [2][kBN]
-  float *red = mask_s + 2 * kBN;                                               // [4][D + 2] warp partials
+  // Three tiles of keys and values in flight per CTA: a CTA usually owns three tiles in all
+  // (see pick of nsplit on the host), so its whole key range is requested up front and the
+  // HBM latency is paid once instead of once per tile.
+  const uint32_t k_s = smem_u32(smem), v_s = k_s + kDecodeStages * kTileBytes;
+  float *mask_s = reinterpret_cast<float *>(smem + 2 * kDecodeStages * kTileBytes);   // [stages][kBN]
+  float *red = mask_s + kDecodeStages * kBN;                                   // [4][D + 2] warp partials
   __shared__ int s_last;
 
   griddep_wait();
@@ -295,8 +308,10 @@ attention_decode_kernel(const AttnParams p) {
       mask_s[buf * kBN + threadIdx.x] = (mb && j < Sk) ? to_f32<T>(mb[j]) * kLog2e : 0.f;
     }
   };
-  if (tile0 < tile1) load_kv(tile0, 0);
-  cp_async_commit();
+  for (int i = 0; i < kDecodeStages - 1; ++i) {
+    if (tile0 + i < tile1) load_kv(tile0 + i, i);
+    cp_async_commit();
+  }
 
   // A fragments of the single query row (row 0 of the 16-row MMA tile; the other rows are zero)
   uint32_t qf[D / 16][4];
@@ -315,10 +330,10 @@ attention_decode_kernel(const AttnParams p) {
   const float sc = p.scale * kLog2e;
 
   for (int n = tile0; n < tile1; ++n) {
-    const int buf = (n - tile0) & 1;
-    if (n + 1 < tile1) load_kv(n + 1, buf ^ 1);
+    const int buf = (n - tile0) % kDecodeStages;
+    if (n + kDecodeStages - 1 < tile1) load_kv(n + kDecodeStages - 1, (buf + kDecodeStages - 1) % kDecodeStages);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<kDecodeStages - 1>();
     __syncthreads();
     const uint32_t kt = k_s + buf * kTileBytes, vt = v_s + buf * kTileBytes;
     // this warp's 16 keys of the tile: two 8-key n-tiles
@@ -447,7 +462,8 @@ template <typename T, int D> int launch_prefill(const AttnParams &p, cudaStream_
 }
 
 template <typename T, int D> int launch_decode(const AttnParams &p, cudaStream_t st) {
-  constexpr size_t smem = 4 * (size_t)kBN * D * 2 + 2 * kBN * sizeof(float) + 4 * (D + 2) * sizeof(float);
+  constexpr size_t smem = 2 * kDecodeStages * (size_t)kBN * D * 2 + kDecodeStages * kBN * sizeof(float) +
+                          4 * (D + 2) * sizeof(float);
   auto kern = attention_decode_kernel<T, D>;
   static bool configured[64] = {};
   int dev = 0;
