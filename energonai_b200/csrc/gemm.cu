@@ -76,7 +76,7 @@ struct GemmParams {
   int out_f32;                   // 1: C is fp32, else the input type
   float *partial;                // swap mode: stream-K partial sums [cta][2][BN][128]
   int *counters;                 // swap mode: one arrival counter per 128-row tile, zero between calls
-  long long units_per_cta;       // swap mode: stream-K units (one unit = one pipeline stage of one tile) per CTA
+  int units_per_cta;             // swap mode: stream-K units (one unit = one pipeline stage of one tile) per CTA
   int stages;                    // pipeline depth actually used (<= kMaxStages)
   int kpb;                       // k-blocks (64 columns each) per pipeline stage / barrier hand-over
   int static_w;                  // W may be read before the preceding kernel of the stream has finished
@@ -205,7 +205,7 @@ struct Segment {
 template <int BN, bool SWAP> struct Scheduler {
   const GemmParams &p;
   int lane_tiles, col_tiles, nsk;
-  long long pos, end;
+  int pos, end;              // 32-bit on purpose: these feed divisions on the critical path
   bool first;
   __device__ Scheduler(const GemmParams &pp) : p(pp) {
     lane_tiles = (p.lane_rows + kLanes - 1) / kLanes;
@@ -213,28 +213,28 @@ template <int BN, bool SWAP> struct Scheduler {
     nsk = (p.kblocks + p.kpb - 1) / p.kpb;
     first = true;
     if (SWAP) {
-      const long long total = (long long)lane_tiles * nsk;
-      pos = (long long)blockIdx.x * p.units_per_cta;
+      const int total = lane_tiles * nsk;
+      pos = (int)blockIdx.x * p.units_per_cta;
       end = pos + p.units_per_cta < total ? pos + p.units_per_cta : total;
     } else {
       pos = blockIdx.x;
-      end = (long long)lane_tiles * col_tiles;
+      end = lane_tiles * col_tiles;
     }
   }
   __device__ bool next(Segment &s) {
     if (pos >= end) return false;
     if (SWAP) {
-      s.lane_tile = (int)(pos / nsk);
+      s.lane_tile = pos / nsk;
       s.col_tile = 0;
-      s.sk0 = (int)(pos % nsk);
-      const long long left = end - pos;
-      s.sk1 = (long long)s.sk0 + left < nsk ? (int)(s.sk0 + left) : nsk;
+      s.sk0 = pos - s.lane_tile * nsk;
+      const int left = end - pos;
+      s.sk1 = s.sk0 + left < nsk ? s.sk0 + left : nsk;
       s.partial = !(s.sk0 == 0 && s.sk1 == nsk);
       s.which = first ? 0 : 1;
       pos += s.sk1 - s.sk0;
     } else {
       const int per_group = kGroup * col_tiles;
-      const int group = (int)(pos / per_group), in_group = (int)(pos % per_group);
+      const int group = pos / per_group, in_group = pos - group * per_group;
       const int first_lane = group * kGroup;
       const int gsz = lane_tiles - first_lane < kGroup ? lane_tiles - first_lane : kGroup;
       s.lane_tile = first_lane + in_group % gsz;
@@ -521,9 +521,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           __threadfence();
           if (!epi_sync()) { alive = false; continue; }
           // CTAs whose unit range intersects this tile
-          const long long t0 = (long long)s.lane_tile * sched.nsk;
-          const int first_cta = (int)(t0 / p.units_per_cta);
-          const int last_cta = (int)((t0 + sched.nsk - 1) / p.units_per_cta);
+          const int t0 = s.lane_tile * sched.nsk;
+          const int first_cta = t0 / p.units_per_cta;
+          const int last_cta = (t0 + sched.nsk - 1) / p.units_per_cta;
           if (threadIdx.x == 64) {
             const int arrived = atomicAdd(p.counters + s.lane_tile, 1);
             const int is_last = arrived == last_cta - first_cta;
@@ -537,14 +537,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
             __threadfence();
 #pragma unroll
             for (int m = 0; m < BN; ++m) v[m] = 0.f;
-#pragma unroll 2
-            for (int cta = first_cta; cta <= last_cta; ++cta) {
-              // a CTA's piece of this tile is its first segment iff its range starts inside the tile
-              const int which = ((long long)cta * p.units_per_cta) / sched.nsk == s.lane_tile ? 0 : 1;
-              const float *theirs = p.partial + ((size_t)(cta * 2 + which) * BN) * kLanes;
+            // contributors are read four at a time (all their loads in flight together) and
+            // added in CTA order, so the sum does not depend on which CTA arrived last
+            constexpr int kBatch = BN <= 16 ? 4 : (BN <= 32 ? 2 : 1);
+            for (int c0 = first_cta; c0 <= last_cta; c0 += kBatch) {
+              float t[kBatch][BN];
 #pragma unroll
-              for (int m = 0; m < BN; ++m)
-                if (m < p.M) v[m] += __ldcg(theirs + (size_t)m * kLanes + lrow);
+              for (int j = 0; j < kBatch; ++j) {
+                const int cta = c0 + j;
+                if (cta <= last_cta) {
+                  const int which = cta * p.units_per_cta >= t0 ? 0 : 1;   // its range starts inside this tile
+                  const float *theirs = p.partial + ((size_t)(cta * 2 + which) * BN) * kLanes;
+#pragma unroll
+                  for (int m = 0; m < BN; ++m)
+                    if (m < p.M) t[j][m] = __ldcg(theirs + (size_t)m * kLanes + lrow);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < kBatch; ++j)
+                if (c0 + j <= last_cta) {
+#pragma unroll
+                  for (int m = 0; m < BN; ++m)
+                    if (m < p.M) v[m] += t[j][m];
+                }
             }
           }
         }
@@ -688,13 +703,13 @@ int launch(const CUtensorMap &tl, const CUtensorMap &tc, const GemmParams &p, in
 inline int swap_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
 
 // Stream-K split of the swapped orientation: grid and units (pipeline stages of a tile) per CTA.
-inline void swap_split(int N, int K, int kpb, int *grid, long long *units) {
+inline void swap_split(int N, int K, int kpb, int *grid, int *units) {
   const long long tiles = (N + kLanes - 1) / kLanes, kblocks = (K + kBlockK - 1) / kBlockK;
   const long long nsk = (kblocks + kpb - 1) / kpb;
   const long long total = tiles * nsk;
   long long g = sm_count();
   if (g > total / 2) g = total / 2 > 0 ? total / 2 : 1;   // at least two stages per CTA
-  *units = (total + g - 1) / g;
+  *units = (int)((total + g - 1) / g);
   *grid = (int)((total + *units - 1) / *units);
 }
 
@@ -776,6 +791,7 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
     stages = stages > kMaxStages ? kMaxStages : (stages < 2 ? 2 : stages);
     p.stages = stages;
     const size_t smem = fixed + (size_t)stages * stage_bytes;
+    EB_REQUIRE((long long)((N + kLanes - 1) / kLanes) * ((K + kBlockK - 1) / kBlockK) < (1ll << 30), "gemm: N*K too large");
     swap_split(N, K, p.kpb, &grid, &p.units_per_cta);
     const size_t tiles = (N + kLanes - 1) / kLanes;
     EB_REQUIRE(tiles * sizeof(int) <= kCounterBytes, "gemm: N=%d exceeds the decode path's tile-counter capacity", N);
