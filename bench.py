@@ -218,7 +218,12 @@ def run_ours(args):
         ctx = tp.init_tp(world)
         if os.environ.get("EB_PEER", "1") != "0":
             # generation steps: all-reduce fused into the row-parallel GEMM epilogue (NVLink peer stores)
-            ctx.enable_peer_exchange(CFG["batch"], CFG["hidden"])
+            try:
+                ctx.enable_peer_exchange(CFG["batch"], CFG["hidden"])
+            except Exception as e:          # no peer mapping on this box: NCCL carries every all-reduce
+                ctx.peer = None
+                if rank == 0:
+                    print(f"peer exchange unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
     cfg = dict(CFG)
     if args.layers:
         cfg["depth"] = args.layers

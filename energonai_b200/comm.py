@@ -25,7 +25,7 @@ class PeerExchange:
         self.max_rows, self.max_cols = max_rows, max_cols
         self.recv_bytes = lib().eb_gemm_allreduce_recv_bytes(world, max_rows, max_cols)
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.recv = symm_mem.empty(self.recv_bytes // 4, dtype=torch.float32, device=dev)
+        self.recv = symm_mem.empty(max(self.recv_bytes // 4, 4), dtype=torch.float32, device=dev)
         self.flags = symm_mem.empty(2 * world * FLAG_SLOTS, dtype=torch.int32, device=dev)
         self.recv.zero_()
         self.flags.zero_()
@@ -39,7 +39,9 @@ class PeerExchange:
         dist.barrier(group=group)          # nobody sends before every area is zeroed and mapped
 
     def fits(self, rows, cols):
-        return rows <= 128 and rows * cols <= self.max_rows * self.max_cols and (cols + 127) // 128 <= FLAG_SLOTS
+        from ._lib import lib
+        need = lib().eb_gemm_allreduce_recv_bytes(self.world, rows, cols)
+        return 0 < rows <= 128 and 0 < need <= self.recv_bytes and (cols + 127) // 128 <= FLAG_SLOTS
 
     def next_parity(self):
         p = self.calls & 1

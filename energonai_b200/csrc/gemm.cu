@@ -50,12 +50,13 @@ constexpr uint32_t kBarrierBytes = 1024;      // head of shared memory: mbarrier
 __device__ int g_status[4];      // [0] code (0 = ok), [1] where, [2] block, [3] detail
 
 // Peer exchange of the fused row-parallel GEMM + all-reduce (generation orientation only).
-// Every rank owns a receive area [2 parities][world sources][M][N] fp32 and a flag area
-// [2][world][tiles] u32 in memory its peers can address over NVLink.
+// Every rank owns a receive area [2 parities][world sources][tiles][128 rows][BN] in the operand
+// type (a thread's BN batch values are contiguous, so it moves them with 16-byte accesses) and a
+// flag area [2][world][tiles] u32, both in memory its peers can address over NVLink.
 struct CommParams {
   int rank, world;               // world <= 1: no exchange
   int parity;                    // alternates between consecutive calls (double buffering)
-  float *recv[8];                // recv[r]: base of rank r's receive area (recv[rank] is local)
+  void *recv[8];                 // recv[r]: base of rank r's receive area (recv[rank] is local)
   uint32_t *flags[8];            // flags[r]: base of rank r's flag area
   int max_tiles;                 // flag slots per (parity, source)
 };
@@ -569,14 +570,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           // per destination, wait (bounded) for the flags of all sources in the local area,
           // then sum the sources in rank order, identically on every rank.
           const CommParams &cm = p.comm;
-          const size_t slot = (size_t)p.M * p.N;                        // floats per (parity, source)
-          const size_t my_off = ((size_t)cm.parity * cm.world + cm.rank) * slot;
-          if (n_ok) {
-            for (int r = 0; r < cm.world; ++r) {
-              float *dst = cm.recv[r] + my_off + n;
+          const int tiles = (p.N + kLanes - 1) / kLanes;
+          const size_t slot = (size_t)tiles * kLanes * BN;                // elements per (parity, source)
+          const size_t row_off = ((size_t)s.lane_tile * kLanes + lrow) * BN;
+          const size_t my_off = ((size_t)cm.parity * cm.world + cm.rank) * slot + row_off;
+          {
+            // partial sums travel in the operand type (as an NCCL all-reduce of the product would)
+            uint4 packed[BN / 8];
 #pragma unroll
-              for (int m = 0; m < BN; ++m)
-                if (m < p.M) dst[(size_t)m * p.N] = v[m];
+            for (int q = 0; q < BN / 8; ++q) {
+              Vec16<T> pk;
+              float tmp[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) tmp[j] = v[q * 8 + j];
+              pk.pack(tmp);
+              packed[q] = pk.raw;
+            }
+            for (int r = 0; r < cm.world; ++r) {
+              uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(cm.recv[r]) + my_off);
+#pragma unroll
+              for (int q = 0; q < BN / 8; ++q) dst[q] = packed[q];
             }
           }
           __threadfence_system();
@@ -605,14 +618,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           }
           if (!epi_sync()) { alive = false; continue; }
           if (*abort_flag) { alive = false; continue; }
-          if (n_ok) {
-            const float *src = cm.recv[cm.rank] + (size_t)cm.parity * cm.world * slot + n;
+          {
+            const T *src = reinterpret_cast<const T *>(cm.recv[cm.rank]) + (size_t)cm.parity * cm.world * slot + row_off;
 #pragma unroll
             for (int m = 0; m < BN; ++m) v[m] = 0.f;
             for (int r = 0; r < cm.world; ++r) {
+              const uint4 *sp = reinterpret_cast<const uint4 *>(src + (size_t)r * slot);
 #pragma unroll
-              for (int m = 0; m < BN; ++m)
-                if (m < p.M) v[m] += ld_relaxed_sys_f32(src + (size_t)r * slot + (size_t)m * p.N);
+              for (int q = 0; q < BN / 8; ++q) {
+                Vec16<T> pk;
+                asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(pk.raw.x), "=r"(pk.raw.y), "=r"(pk.raw.z), "=r"(pk.raw.w)
+                             : "l"(sp + q)
+                             : "memory");
+                float tmp[8];
+                pk.unpack(tmp);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[q * 8 + j] += tmp[j];
+              }
             }
           }
         }
@@ -842,7 +865,9 @@ extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ld
 }
 
 extern "C" size_t eb_gemm_allreduce_recv_bytes(int world, int M, int N) {
-  return (size_t)2 * world * M * N * sizeof(float);
+  if (M <= 0 || M > kLanes || N <= 0 || world <= 0) return 0;
+  const size_t tiles = (N + kLanes - 1) / kLanes;
+  return (size_t)2 * world * tiles * kLanes * swap_bn(M) * 2;     // 16-bit elements
 }
 
 extern "C" int eb_gemm_allreduce(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
@@ -862,7 +887,7 @@ extern "C" int eb_gemm_allreduce(const void *A, long long lda, const void *W, lo
                "gemm_allreduce: receive areas of %zu bytes are too small for world %d, M %d, N %d", recv_bytes, world, M, N);
     for (int r = 0; r < world; ++r) {
       EB_REQUIRE(peer_recv[r] && peer_flags[r], "gemm_allreduce: null exchange area for rank %d", r);
-      cm.recv[r] = reinterpret_cast<float *>(peer_recv[r]);
+      cm.recv[r] = peer_recv[r];
       cm.flags[r] = reinterpret_cast<uint32_t *>(peer_flags[r]);
     }
   }

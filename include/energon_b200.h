@@ -177,9 +177,9 @@ EB_API size_t eb_gemm_workspace_bytes(int M, int N, int K);
  * bytes (or more) and a flag area of 2*world*flag_slots_per_source uint32 (zero before first
  * use), both addressable by its peers (NVLink peer mapping); peer_recv[r] / peer_flags[r] are
  * HOST arrays of `world` device pointers to rank r's areas as mapped in this process.  The CTA
- * that completes a tile stores its fp32 partial into every rank's receive area with plain peer
- * stores, publishes one flag per destination, waits (bounded, 1 s, see eb_device_status) for all
- * sources' flags in its own area, and sums the sources in rank order, so every rank obtains the
+ * that completes a tile stores its partial (rounded to the operand type, as an all-reduce of the
+ * product would see it) into every rank's receive area with plain 16-byte peer stores, publishes one flag per destination, waits (bounded, 1 s, see eb_device_status) for all
+ * sources' flags in its own area, and sums the sources in fp32 in rank order, so every rank obtains the
  * bit-identical result; bias, activation and residual are applied after the sum on every rank.
  * `parity` must alternate (0,1,0,1,...) over the successive calls that share the areas, in the
  * same order on all ranks.  world == 1 degenerates to eb_gemm. */
