@@ -15,6 +15,11 @@ constexpr int kThreads = 128;
 
 template <typename T, int VEC> struct alignas(sizeof(T) * VEC > 16 ? 16 : sizeof(T) * VEC) Pack { T e[VEC]; };
 
+// The row is kept in registers as the raw 16-byte packs that were loaded (half the registers of
+// an fp32 copy for 16-bit inputs), and unpacked again in each of the three passes: more rows are
+// in flight per SM, which is what a bandwidth-bound kernel with a two-reduction latency chain
+// per row needs.  With fused operands the sum is formed once, rounded to the input type (that is
+// what the residual stream stores) and kept as the pack.
 template <typename Tin, typename Tout, int MAXV>
 __global__ void __launch_bounds__(kThreads)
 ln_cached_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restrict__ invvar,
@@ -29,47 +34,61 @@ ln_cached_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restri
   griddep_launch();
   const int packs = n2 / VEC;
   const float inv_n = 1.f / (float)n2;
+  const bool fused = residual != nullptr || bias != nullptr;
   for (long long row = blockIdx.x; row < n1; row += gridDim.x) {
     const PI *xr = reinterpret_cast<const PI *>(x + row * n2);
     const PI *rr = residual ? reinterpret_cast<const PI *>(residual + row * n2) : nullptr;
-    float v[MAXV][VEC];
-    float s = 0.f;
+    PI v[MAXV];
 #pragma unroll
     for (int t = 0; t < MAXV; ++t) {
       const int p = threadIdx.x + t * kThreads;
-      if (p < packs) {
-        PI a = xr[p];
+      if (p < packs) v[t] = xr[p];
+    }
+    if (fused) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) v[t][e] = to_f32<Tin>(a.e[e]);
-        if (rr) {
-          PI r = rr[p];
+      for (int t = 0; t < MAXV; ++t) {
+        const int p = threadIdx.x + t * kThreads;
+        if (p < packs) {
+          float f[VEC];
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) v[t][e] += to_f32<Tin>(r.e[e]);
+          for (int e = 0; e < VEC; ++e) f[e] = to_f32<Tin>(v[t].e[e]);
+          if (rr) {
+            const PI r = rr[p];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) f[e] += to_f32<Tin>(r.e[e]);
+          }
+          if (bias) {
+            const PI bb = reinterpret_cast<const PI *>(bias)[p];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) f[e] += to_f32<Tin>(bb.e[e]);
+          }
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) v[t].e[e] = from_f32<Tin>(f[e]);
+          if (sum_out) reinterpret_cast<PI *>(sum_out + row * n2)[p] = v[t];
         }
-        if (bias) {
-          PI bb = reinterpret_cast<const PI *>(bias)[p];
+      }
+    } else if (sum_out) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) v[t][e] += to_f32<Tin>(bb.e[e]);
-        }
-        if (sum_out) {
-          // the residual stream continues in the input precision: normalise what is stored
-          PI o;
+      for (int t = 0; t < MAXV; ++t) {
+        const int p = threadIdx.x + t * kThreads;
+        if (p < packs) reinterpret_cast<PI *>(sum_out + row * n2)[p] = v[t];
+      }
+    }
+    float s = 0.f;
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) { o.e[e] = from_f32<Tin>(v[t][e]); v[t][e] = to_f32<Tin>(o.e[e]); }
-          reinterpret_cast<PI *>(sum_out + row * n2)[p] = o;
-        }
+    for (int t = 0; t < MAXV; ++t) {
+      if (threadIdx.x + t * kThreads < packs) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) s += v[t][e];
+        for (int e = 0; e < VEC; ++e) s += to_f32<Tin>(v[t].e[e]);
       }
     }
     const float mu = block_sum<kThreads>(s, scratch) * inv_n;
     float q = 0.f;
 #pragma unroll
     for (int t = 0; t < MAXV; ++t) {
-      const int p = threadIdx.x + t * kThreads;
-      if (p < packs) {
+      if (threadIdx.x + t * kThreads < packs) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) { const float d = v[t][e] - mu; q += d * d; }
+        for (int e = 0; e < VEC; ++e) { const float d = to_f32<Tin>(v[t].e[e]) - mu; q += d * d; }
       }
     }
     const float var = block_sum<kThreads>(q, scratch) * inv_n;
@@ -81,13 +100,13 @@ ln_cached_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restri
       if (p < packs) {
         PO o;
         if (gamma) {
-          PO g = reinterpret_cast<const PO *>(gamma)[p], bt = reinterpret_cast<const PO *>(beta)[p];
+          const PO g = reinterpret_cast<const PO *>(gamma)[p], bt = reinterpret_cast<const PO *>(beta)[p];
 #pragma unroll
           for (int e = 0; e < VEC; ++e)
-            o.e[e] = from_f32<Tout>(to_f32<Tout>(g.e[e]) * ((v[t][e] - mu) * iv) + to_f32<Tout>(bt.e[e]));
+            o.e[e] = from_f32<Tout>(to_f32<Tout>(g.e[e]) * ((to_f32<Tin>(v[t].e[e]) - mu) * iv) + to_f32<Tout>(bt.e[e]));
         } else {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) o.e[e] = from_f32<Tout>((v[t][e] - mu) * iv);
+          for (int e = 0; e < VEC; ++e) o.e[e] = from_f32<Tout>((to_f32<Tin>(v[t].e[e]) - mu) * iv);
         }
         yr[p] = o;
       }
@@ -151,7 +170,7 @@ template <typename Tin, typename Tout>
 int launch_ln(void *y, float *mean, float *invvar, const void *x, const void *residual, const void *bias,
               void *sum_out, const void *gamma, const void *beta, long long n1, int n2, float eps, cudaStream_t st) {
   constexpr int VEC = 16 / sizeof(Tin);
-  const long long cap = (long long)sm_count() * 16;
+  const long long cap = (long long)sm_count() * 32;
   const int grid = (int)(n1 < cap ? n1 : cap);
   const bool vec_ok = n2 % VEC == 0 && aligned16(x) && aligned16(y) && aligned16(residual) && aligned16(bias) &&
                       aligned16(sum_out) && aligned16(gamma) && aligned16(beta) &&

@@ -25,14 +25,17 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
                float scale) {
   using P = Pack<T, VEC>;
   const int lane = threadIdx.x & 31;
-  const long long rows = (long long)B * H * S;
-  const long long warp0 = (long long)blockIdx.x * kWarps + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * kWarps;
+  // blockIdx.y = batch entry; rows of one batch entry (head, query) are walked with 32-bit
+  // arithmetic (64-bit divisions per row were a visible part of the row's latency chain)
+  const int b = blockIdx.y;
+  const unsigned rows_b = (unsigned)H * (unsigned)S;
+  const unsigned warp0 = blockIdx.x * kWarps + (threadIdx.x >> 5), nwarps = gridDim.x * kWarps;
   const int packs_row = S / VEC;   // S % VEC == 0 on this path
-  for (long long row = warp0; row < rows; row += nwarps) {
-    const int i = (int)(row % S);
-    const int b = (int)(row / ((long long)H * S));
-    int len = real_len[b];
-    len = len < 0 ? 0 : (len > S ? S : len);
+  int len = real_len[b];
+  len = len < 0 ? 0 : (len > S ? S : len);
+  for (unsigned rb = warp0; rb < rows_b; rb += nwarps) {
+    const int i = (int)(rb % (unsigned)S);
+    const long long row = (long long)b * rows_b + rb;
     if (i >= len && !(flags & EB_SM_ALLROWS)) continue;
     int nvis = S;
     if (flags & EB_SM_CAUSAL) nvis = min(nvis, i + 1);
@@ -54,17 +57,16 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
         }
       }
       mx = warp_max(mx);
+      // exp is evaluated twice (once for the sum, once for the output) instead of keeping the
+      // fp32 exponentials: fewer registers, more rows in flight per SM
       float sum = 0.f;
-      float ex[VPL > 0 ? VPL : 1][VEC];
 #pragma unroll
       for (int t = 0; t < VPL; ++t) {
         const int v = lane + 32 * t;
+        if (v < packs_vis) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          float p = 0.f;
-          if (v < packs_vis && v * VEC + e < nvis) p = __expf(to_f32<T>(cache[t].e[e]) * scale - mx);
-          ex[t][e] = p;
-          sum += p;
+          for (int e = 0; e < VEC; ++e)
+            if (v * VEC + e < nvis) sum += __expf(to_f32<T>(cache[t].e[e]) * scale - mx);
         }
       }
       sum = warp_sum(sum);
@@ -75,7 +77,11 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
         if (v < packs_row) {
           P out;
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) out.e[e] = from_f32<T>(ex[t][e] * inv);
+          for (int e = 0; e < VEC; ++e) {
+            float p = 0.f;
+            if (v < packs_vis && v * VEC + e < nvis) p = __expf(to_f32<T>(cache[t].e[e]) * scale - mx) * inv;
+            out.e[e] = from_f32<T>(p);
+          }
           rp[v] = out;
         }
       }
@@ -115,10 +121,12 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
 template <typename T>
 int launch_softmax(void *scores, const int32_t *real_len, int B, int S, int H, int flags, float scale,
                    cudaStream_t st) {
-  const long long rows = (long long)B * H * S;
-  long long g = (rows + kWarps - 1) / kWarps;
-  const long long cap = (long long)sm_count() * 32;
-  const int grid = (int)(g < cap ? g : cap);
+  const long long rows_b = (long long)H * S;
+  long long gx = (rows_b + kWarps - 1) / kWarps;
+  const long long cap = ((long long)sm_count() * 32 + B - 1) / B;
+  if (gx > cap) gx = cap;
+  if (gx < 1) gx = 1;
+  const dim3 grid((unsigned)gx, (unsigned)B);
   constexpr int N = 16 / sizeof(T);
   T *p = reinterpret_cast<T *>(scores);
 #define EB_SM_LAUNCH(VEC, VPL) \
@@ -148,6 +156,7 @@ extern "C" int eb_scale_mask_softmax(void *scores, const int32_t *real_seq_len, 
   using namespace eb;
   EB_REQUIRE(dtype_ok(dtype), "scale_mask_softmax: bad dtype %d", dtype);
   EB_REQUIRE(batch >= 0 && seq_len >= 0 && head_num >= 0, "scale_mask_softmax: negative size");
+  EB_REQUIRE(batch <= 65535 && (long long)head_num * seq_len < (1ll << 31), "scale_mask_softmax: batch > 65535 or heads*seq too large");
   EB_REQUIRE((flags & ~7) == 0, "scale_mask_softmax: unknown flag bits 0x%x", flags);
   if ((long long)batch * seq_len * head_num == 0) return EB_OK;
   EB_REQUIRE(scores && real_seq_len, "scale_mask_softmax: null pointer");

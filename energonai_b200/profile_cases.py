@@ -3,6 +3,7 @@
     python -m energonai_b200.profile_cases gemm_decode      # the four OPT-13B generation-step GEMM shapes
     python -m energonai_b200.profile_cases gemm_prefill     # one 8192-row prompt GEMM
     python -m energonai_b200.profile_cases attention        # prompt and generation-step attention
+    python -m energonai_b200.profile_cases membound         # event-timed GB/s of the memory-bound kernels
 
 Each case holds a few hundred MB on the device (more than L2, so DRAM counters are
 meaningful) and launches each kernel a handful of times.
@@ -47,5 +48,75 @@ def attention():
     print("attention", tuple(o.shape), tuple(o2.shape))
 
 
+
+
+def membound():
+    """CUDA-event timings of the memory-bound kernels at benchmark shapes (configuration 2:
+    batch 32 x 512, hidden 1024, 16 heads; configuration 3 prompt pass: 8192 x 5120), reported as
+    algorithmic GB/s.  Inputs are larger than L2 or the L2 is flushed between repetitions."""
+    import numpy as np
+    from . import kernel as EK
+    from .kernel.cuda_native.layer_norm import layer_norm_forward
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, reps=5):
+        fn()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / reps
+
+    def report(name, nbytes, ms):
+        print(f"{name}: {ms * 1e3:.1f} us, {nbytes / 1e6:.1f} MB algorithmic, {nbytes / ms / 1e6:.0f} GB/s")
+
+    # the copies run at 8x configuration 2's batch so that a launch lasts ~100 us and the
+    # ~10 us of host launch latency inside the event bracket stops mattering
+    B, S, H, D = 256, 512, 16, 64
+    h = H * D
+    rng = np.random.default_rng(1)
+    lens = torch.from_numpy(rng.integers(32, S + 1, B).astype(np.int32)).cuda()
+    V = int(lens.sum())
+    valid = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tmp = torch.zeros(B, S, dtype=torch.int32, device="cuda")
+    moff = torch.zeros(B, S, dtype=torch.int32, device="cuda")
+    x = torch.randn(B, S, h, device="cuda", dtype=torch.float16)
+    report("ft_build_padding_offsets B=256 S=512", 4 * B + 4 * V + 4,
+           timed(lambda: EK.ft_build_padding_offsets(lens, B, S, valid, tmp)))
+    report("ft_remove_padding", 2 * V * h * 2 + 8 * V, timed(lambda: EK.ft_remove_padding(x, tmp, moff, V, h)))
+    packed = EK.ft_remove_padding(x, tmp, moff, V, h)
+    report("ft_rebuild_padding (zero rows included)", (V + B * S) * h * 2 + 4 * V,
+           timed(lambda: EK.ft_rebuild_padding(packed, moff, V, h, B, S)))
+    bufs = [torch.zeros(B, H, S, D, device="cuda", dtype=torch.float16) for _ in range(3)]
+    p4 = packed.view(1, V, H, D)
+    report("ft_transpose_rebuild_padding (3 tensors)", 3 * 2 * V * h * 2 + 4 * V,
+           timed(lambda: EK.ft_transpose_rebuild_padding(p4, p4, p4, *bufs, B, S, H, D, V, moff)))
+    report("ft_transpose_remove_padding", 2 * V * h * 2 + 4 * V,
+           timed(lambda: EK.ft_transpose_remove_padding(bufs[0], V, B, S, H, D, moff)))
+    report("transpose_pad", (V + B * S) * h * 2, timed(lambda: EK.transpose_pad(p4, B, S, lens, H, D)))
+    report("transpose_depad", 2 * V * h * 2, timed(lambda: EK.transpose_depad(bufs[0], B, V, S, lens, H, D)))
+    del bufs, x, packed, p4
+    B = 32
+    lens = lens[:B].contiguous()
+    V = int(lens.sum())
+    scores = torch.randn(B, H, S, S, device="cuda", dtype=torch.float16)
+    vis = int(sum(int(l) * (int(l) + 1) // 2 for l in lens.tolist()))
+    report("scale_mask_softmax [32,16,512,512] fp16 (visible reads + row writes)", (vis + V * S) * H * 2,
+           timed(lambda: EK.scale_mask_softmax(B, S, H, scores, lens)))
+    for rows, n in ((B * S, 1024), (8192, 5120)):
+        xx = torch.randn(rows, n, device="cuda", dtype=torch.float16)
+        g, b = torch.ones(n, device="cuda", dtype=torch.float16), torch.zeros(n, device="cuda", dtype=torch.float16)
+        report(f"layer_norm {rows} x {n} fp16", 2 * rows * n * 2, timed(lambda: layer_norm_forward(xx, g, b, 1e-5)))
+        rr = torch.randn_like(xx)
+        report(f"layer_norm + residual + bias + sum_out {rows} x {n}", 4 * rows * n * 2,
+               timed(lambda: layer_norm_forward(xx, g, b, 1e-5, residual=rr, add_bias=b, return_sum=True)))
+
+
 if __name__ == "__main__":
-    {"gemm_decode": gemm_decode, "gemm_prefill": gemm_prefill, "attention": attention}[sys.argv[1]]()
+    {"gemm_decode": gemm_decode, "gemm_prefill": gemm_prefill, "attention": attention, "membound": membound}[sys.argv[1]]()

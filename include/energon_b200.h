@@ -128,6 +128,7 @@ EB_API int eb_scale_mask_softmax(void *scores, const int32_t *real_seq_len, int 
  * layer_norm_cuda_kernel.cu:243-279) and the LayerNorm1D modules of the block
  * (energonai/model/endecoder.py:28,39).  Rows n1, row length n2.
  *   t   = x (+ residual) (+ bias[n2])            (optional operands may be NULL)
+ *   with residual or bias, t is rounded to in_dtype first (what a residual stream stores);
  *   sum_out = t (in in_dtype), if sum_out != NULL
  *   y   = gamma * (t - mean) * invvar + beta     (gamma/beta NULL: no affine)
  *   mean[n1], invvar[n1] fp32, if non-NULL.
