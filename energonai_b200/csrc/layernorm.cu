@@ -3,7 +3,8 @@
 // One CTA of 128 threads per row.  The row (after the optional adds) is loaded once in
 // 16-byte vectors into fp32 registers; mean and the centred second moment are each one
 // block reduction over the register copy (two-pass, so no cancellation), and the output is
-// written once.  HBM traffic is therefore the algorithmic minimum: one read of every input
+// written once (statistics: one reduction of the sum and the sum of squares of the row shifted
+// by its first element).  HBM traffic is therefore the algorithmic minimum: one read of every input
 // operand and one write of every output.  Rows that do not fit the register budget, or that
 // are not 16-byte aligned, take a three-pass variant that re-reads the operands.
 #include "common.cuh"
@@ -20,7 +21,12 @@ template <typename T, int VEC> struct alignas(sizeof(T) * VEC > 16 ? 16 : sizeof
 // in flight per SM, which is what a bandwidth-bound kernel with a two-reduction latency chain
 // per row needs.  With fused operands the sum is formed once, rounded to the input type (that is
 // what the residual stream stores) and kept as the pack.
-template <typename Tin, typename Tout, int MAXV>
+// G threads cooperate on one row: G = 128 (the whole CTA, long rows) or G = 32 (one warp per row,
+// four rows per CTA and no block-wide synchronisation, for rows that fit 32 lanes x MAXV packs).
+// Mean and variance come from one reduction of (sum, sum of squares) of the row shifted by its
+// first element, which keeps the single pass free of cancellation for the value ranges a
+// residual stream has.
+template <typename Tin, typename Tout, int MAXV, int G>
 __global__ void __launch_bounds__(kThreads)
 ln_cached_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restrict__ invvar,
                  const Tin *__restrict__ x, const Tin *__restrict__ residual, const Tin *__restrict__ bias,
@@ -29,25 +35,31 @@ ln_cached_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restri
   constexpr int VEC = 16 / sizeof(Tin);
   using PI = Pack<Tin, VEC>;
   using PO = Pack<Tout, VEC>;
-  __shared__ float scratch[kThreads / 32];
+  __shared__ float scratch[2 * (kThreads / 32)];
   griddep_wait();
   griddep_launch();
   const int packs = n2 / VEC;
   const float inv_n = 1.f / (float)n2;
   const bool fused = residual != nullptr || bias != nullptr;
-  for (long long row = blockIdx.x; row < n1; row += gridDim.x) {
-    const PI *xr = reinterpret_cast<const PI *>(x + row * n2);
-    const PI *rr = residual ? reinterpret_cast<const PI *>(residual + row * n2) : nullptr;
+  constexpr int kRowsPerCta = kThreads / G;
+  const int gtid = threadIdx.x % G;
+  // every thread of a CTA runs the same number of iterations (the block reduction synchronises)
+  for (long long row0 = (long long)blockIdx.x * kRowsPerCta; row0 < n1; row0 += (long long)gridDim.x * kRowsPerCta) {
+    const long long row = row0 + threadIdx.x / G;
+    const bool live = row < n1;
+    const long long rsafe = live ? row : 0;
+    const PI *xr = reinterpret_cast<const PI *>(x + rsafe * n2);
+    const PI *rr = residual ? reinterpret_cast<const PI *>(residual + rsafe * n2) : nullptr;
     PI v[MAXV];
 #pragma unroll
     for (int t = 0; t < MAXV; ++t) {
-      const int p = threadIdx.x + t * kThreads;
+      const int p = gtid + t * G;
       if (p < packs) v[t] = xr[p];
     }
     if (fused) {
 #pragma unroll
       for (int t = 0; t < MAXV; ++t) {
-        const int p = threadIdx.x + t * kThreads;
+        const int p = gtid + t * G;
         if (p < packs) {
           float f[VEC];
 #pragma unroll
@@ -64,40 +76,58 @@ ln_cached_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restri
           }
 #pragma unroll
           for (int e = 0; e < VEC; ++e) v[t].e[e] = from_f32<Tin>(f[e]);
-          if (sum_out) reinterpret_cast<PI *>(sum_out + row * n2)[p] = v[t];
+          if (sum_out && live) reinterpret_cast<PI *>(sum_out + row * n2)[p] = v[t];
         }
       }
     } else if (sum_out) {
 #pragma unroll
       for (int t = 0; t < MAXV; ++t) {
-        const int p = threadIdx.x + t * kThreads;
-        if (p < packs) reinterpret_cast<PI *>(sum_out + row * n2)[p] = v[t];
+        const int p = gtid + t * G;
+        if (p < packs && live) reinterpret_cast<PI *>(sum_out + row * n2)[p] = v[t];
       }
     }
-    float s = 0.f;
+    // shift by the row's first element (same value in every thread of the group)
+    float pivot = to_f32<Tin>(v[0].e[0]);
+    if (G == 32) {
+      pivot = __shfl_sync(0xffffffffu, pivot, 0);
+    } else {
+      __syncthreads();
+      if (threadIdx.x == 0) scratch[0] = pivot;
+      __syncthreads();
+      pivot = scratch[0];
+    }
+    float s = 0.f, q = 0.f;
 #pragma unroll
     for (int t = 0; t < MAXV; ++t) {
-      if (threadIdx.x + t * kThreads < packs) {
+      if (gtid + t * G < packs) {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) s += to_f32<Tin>(v[t].e[e]);
+        for (int e = 0; e < VEC; ++e) { const float d = to_f32<Tin>(v[t].e[e]) - pivot; s += d; q += d * d; }
       }
     }
-    const float mu = block_sum<kThreads>(s, scratch) * inv_n;
-    float q = 0.f;
-#pragma unroll
-    for (int t = 0; t < MAXV; ++t) {
-      if (threadIdx.x + t * kThreads < packs) {
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) { const float d = to_f32<Tin>(v[t].e[e]) - mu; q += d * d; }
-      }
+    if (G == 32) {
+      s = warp_sum(s);
+      q = warp_sum(q);
+    } else {
+      s = warp_sum(s);
+      q = warp_sum(q);
+      const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+      __syncthreads();
+      if (lane == 0) { scratch[warp] = s; scratch[kThreads / 32 + warp] = q; }
+      __syncthreads();
+      s = lane < kThreads / 32 ? scratch[lane] : 0.f;
+      q = lane < kThreads / 32 ? scratch[kThreads / 32 + lane] : 0.f;
+      s = warp_sum(s);
+      q = warp_sum(q);
     }
-    const float var = block_sum<kThreads>(q, scratch) * inv_n;
+    const float ms = s * inv_n;                       // mean of the shifted row
+    const float mu = pivot + ms;
+    const float var = fmaxf(q * inv_n - ms * ms, 0.f);
     const float iv = rsqrtf(var + eps);
     PO *yr = reinterpret_cast<PO *>(y + row * n2);
 #pragma unroll
     for (int t = 0; t < MAXV; ++t) {
-      const int p = threadIdx.x + t * kThreads;
-      if (p < packs) {
+      const int p = gtid + t * G;
+      if (p < packs && live) {
         PO o;
         if (gamma) {
           const PO g = reinterpret_cast<const PO *>(gamma)[p], bt = reinterpret_cast<const PO *>(beta)[p];
@@ -111,7 +141,7 @@ ln_cached_kernel(Tout *__restrict__ y, float *__restrict__ mean, float *__restri
         yr[p] = o;
       }
     }
-    if (threadIdx.x == 0) {
+    if (gtid == 0 && live) {
       if (mean) mean[row] = mu;
       if (invvar) invvar[row] = iv;
     }
@@ -178,13 +208,23 @@ int launch_ln(void *y, float *mean, float *invvar, const void *x, const void *re
   const int packs = n2 / VEC;
 #define EB_LN_ARGS (Tout *)y, mean, invvar, (const Tin *)x, (const Tin *)residual, (const Tin *)bias, (Tin *)sum_out, \
                    (const Tout *)gamma, (const Tout *)beta, n1, n2, eps
-  if (vec_ok && packs <= kThreads * 16) {
+  if (vec_ok && packs <= 32 * 8 && n1 >= 64) {
+    // short rows, many of them: one warp per row
+    const int need = (packs + 31) / 32;
+    const long long ctas = (n1 + 3) / 4;
+    const int g4 = (int)(ctas < cap ? ctas : cap);
+    if (need <= 1) launch_pdl(ln_cached_kernel<Tin, Tout, 1, 32>, dim3(g4), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else if (need <= 2) launch_pdl(ln_cached_kernel<Tin, Tout, 2, 32>, dim3(g4), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else if (need <= 4) launch_pdl(ln_cached_kernel<Tin, Tout, 4, 32>, dim3(g4), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else launch_pdl(ln_cached_kernel<Tin, Tout, 8, 32>, dim3(g4), dim3(kThreads), 0, st, EB_LN_ARGS);
+  } else if (vec_ok && packs <= kThreads * 16) {
     const int need = (packs + kThreads - 1) / kThreads;
-    if (need <= 1) launch_pdl(ln_cached_kernel<Tin, Tout, 1>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
-    else if (need <= 2) launch_pdl(ln_cached_kernel<Tin, Tout, 2>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
-    else if (need <= 4) launch_pdl(ln_cached_kernel<Tin, Tout, 4>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
-    else if (need <= 8) launch_pdl(ln_cached_kernel<Tin, Tout, 8>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
-    else launch_pdl(ln_cached_kernel<Tin, Tout, 16>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
+    if (need <= 1) launch_pdl(ln_cached_kernel<Tin, Tout, 1, kThreads>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else if (need <= 2) launch_pdl(ln_cached_kernel<Tin, Tout, 2, kThreads>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else if (need <= 4) launch_pdl(ln_cached_kernel<Tin, Tout, 4, kThreads>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else if (need <= 6) launch_pdl(ln_cached_kernel<Tin, Tout, 6, kThreads>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else if (need <= 8) launch_pdl(ln_cached_kernel<Tin, Tout, 8, kThreads>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
+    else launch_pdl(ln_cached_kernel<Tin, Tout, 16, kThreads>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
   } else {
     launch_pdl(ln_generic_kernel<Tin, Tout>, dim3(grid), dim3(kThreads), 0, st, EB_LN_ARGS);
   }

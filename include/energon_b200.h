@@ -132,7 +132,8 @@ EB_API int eb_scale_mask_softmax(void *scores, const int32_t *real_seq_len, int 
  *   sum_out = t (in in_dtype), if sum_out != NULL
  *   y   = gamma * (t - mean) * invvar + beta     (gamma/beta NULL: no affine)
  *   mean[n1], invvar[n1] fp32, if non-NULL.
- * Statistics in fp32 (two-pass over a register-resident row), biased variance. */
+ * Statistics in fp32 over a register-resident row (one pass over the row shifted by its first
+ * element), biased variance. */
 EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x, const void *residual, const void *bias,
                       void *sum_out, const void *gamma, const void *beta, int64_t n1, int n2, double eps, int in_dtype,
                       int out_dtype, void *stream);
