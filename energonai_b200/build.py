@@ -35,7 +35,7 @@ def _newer(src_paths, target):
 def build(force=False, verbose=False):
     os.makedirs(OBJ_DIR, exist_ok=True)
     sources = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".inc"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "energon_b200.h"))
     jobs = []
     for s in sources:

@@ -111,6 +111,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe (try_wait may suspend the thread for a hardware-defined time).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false when the CTA is aborting (this or another role ran out of time).
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int where) {
   const unsigned long long t0 = globaltimer();
@@ -139,6 +151,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+// Asks for a weight tile to be brought into L2 (no shared-memory destination, no completion).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -508,6 +524,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
         float v[BN];
 #pragma unroll
         for (int c = 0; c < BN / 16; ++c) tmem_ld16(t_base + c * 16, v + c * 16);
+        // The residual of this thread's outputs is requested now, all rows at once, so that its
+        // DRAM latency passes during the partial-sum exchange; fetched inside the store loop
+        // below, every load would wait for the store before it (the two may alias).
+        constexpr bool kEarlyRes = BN <= 32;
+        T r_early[kEarlyRes ? BN : 1];
+        const float b = (bias && n_ok) ? to_f32<T>(bias[n]) : 0.f;
+        if (kEarlyRes && res && n_ok) {
+#pragma unroll
+          for (int m = 0; m < (kEarlyRes ? BN : 1); ++m)
+            if (m < p.M) r_early[m] = __ldcg(res + (long long)m * p.ldr + n);
+        }
         // the accumulator is in registers: release it before any global traffic
         tcgen05_fence_before();
         __syncwarp();
@@ -640,15 +667,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           }
         }
         if (do_epilogue && n_ok) {
-          const float b = bias ? to_f32<T>(bias[n]) : 0.f;
 #pragma unroll
-          for (int m = 0; m < BN; ++m) {
-            if (m < p.M) {
-              float x = apply_act(v[m] + b, p.act);
-              if (res) x += to_f32<T>(res[(long long)m * p.ldr + n]);
-              const long long off = c_row_offset(p, m) + n;
-              if (p.out_f32) reinterpret_cast<float *>(p.C)[off] = x;
-              else reinterpret_cast<T *>(p.C)[off] = from_f32<T>(x);
+          for (int m0 = 0; m0 < BN; m0 += 16) {
+            T r_late[16];
+            if (!kEarlyRes && res) {               // 16 rows of residual in flight together
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (m0 + j < p.M) r_late[j] = __ldcg(res + (long long)(m0 + j) * p.ldr + n);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + j;
+              if (m < p.M) {
+                float x = apply_act(v[m] + b, p.act);
+                if (res) x += to_f32<T>(kEarlyRes ? r_early[kEarlyRes ? m : 0] : r_late[j]);
+                const long long off = c_row_offset(p, m) + n;
+                if (p.out_f32) reinterpret_cast<float *>(p.C)[off] = x;
+                else reinterpret_cast<T *>(p.C)[off] = from_f32<T>(x);
+              }
             }
           }
         }
@@ -738,10 +774,128 @@ inline void swap_split(int N, int K, int kpb, int *grid, int *units) {
 
 constexpr size_t kCounterBytes = 64 * 1024;   // workspace head: one int per 128-row tile, zero between calls
 
+#include "gemm_chain.cuh"
+
+template <typename T, int BN>
+int launch_chain(const ChainMaps &maps, const ChainParams &p, int grid, size_t smem, cudaStream_t st) {
+  auto kern = chain_kernel<T, BN>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(EB_ECUDA, "decode_chain: cannot reserve shared memory");
+    }
+    configured[dev] = true;
+  }
+  launch_pdl(kern, dim3(grid), dim3(kThreads), smem, st, maps, p);
+  return check_launch("decode_chain");
+}
+
+// Workspace of a chain: [4 KB arrival counters of the operations][kMaxOps x 16 KB tile counters]
+// [stream-K partial sums of the GEMMs, one area each].  Every counter sits at an offset that
+// does not depend on the operations, so chains of different make-up can share one zero-filled
+// workspace: no chain's partial sums ever land on another chain's counters.
+constexpr size_t kChainHeadBytes = 4096, kChainTileCounterBytes = 16384;
+constexpr size_t kChainPartialOffset = kChainHeadBytes + kMaxOps * kChainTileCounterBytes;
+
+inline size_t chain_op_bytes(int grid, int bn) { return (size_t)grid * 2 * bn * kLanes * sizeof(float); }
+
 }  // namespace
 }  // namespace eb
 
 using namespace eb;
+
+extern "C" size_t eb_decode_chain_workspace_bytes(const eb_chain_op *ops, int n_ops, int M) {
+  if (!ops || n_ops <= 0 || n_ops > kMaxOps || M <= 0 || M > kLanes) return 0;
+  size_t total = kChainPartialOffset;
+  for (int i = 0; i < n_ops; ++i)
+    if (ops[i].type == EB_OP_GEMM) total += chain_op_bytes(sm_count(), swap_bn(M));
+  return total;
+}
+
+extern "C" int eb_decode_chain(const eb_chain_op *ops, int n_ops, int M, int dtype, void *workspace,
+                               size_t workspace_bytes, void *stream) {
+  EB_REQUIRE(ops && n_ops >= 1 && n_ops <= kMaxOps, "decode_chain: 1..%d operations", kMaxOps);
+  EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "decode_chain: fp16 or bf16 only");
+  EB_REQUIRE(M >= 1 && M <= kLanes, "decode_chain: M must be in [1, 128] (got %d)", M);
+  const int grid = sm_count();
+  EB_REQUIRE(M <= grid, "decode_chain: M exceeds the number of SMs");
+  const size_t need = eb_decode_chain_workspace_bytes(ops, n_ops, M);
+  EB_REQUIRE(workspace && aligned16(workspace) && workspace_bytes >= need,
+             "decode_chain: needs a workspace of %zu bytes, zero-filled once", need);
+  const int bn = swap_bn(M);
+  ChainParams p{};
+  ChainMaps maps;
+  p.n_ops = n_ops; p.M = M;
+  static const int prefetch_env = getenv("EB_CHAIN_PREFETCH") ? atoi(getenv("EB_CHAIN_PREFETCH")) : -1;
+  p.prefetch = prefetch_env >= 0 ? (prefetch_env > 64 ? 64 : prefetch_env) : 8;
+  p.kpb = bn <= 32 ? 2 : 1;
+  const size_t stage_bytes = ((size_t)kLanes * 128 + (size_t)bn * 128) * p.kpb;
+  int stages = (int)((200 * 1024 - kBarrierBytes - 1024) / stage_bytes);
+  p.stages = stages > kMaxStages ? kMaxStages : (stages < 2 ? 2 : stages);
+  const size_t smem = kBarrierBytes + 1024 + (size_t)p.stages * stage_bytes;
+  p.done = reinterpret_cast<int *>(workspace);
+  // diagnostics: with EB_CHAIN_TRACE=1 and a workspace with room behind the required part, every
+  // CTA leaves globaltimer stamps per operation there
+  static const bool trace_env = getenv("EB_CHAIN_TRACE") && atoi(getenv("EB_CHAIN_TRACE")) > 0;
+  const size_t trace_bytes = (size_t)grid * kMaxOps * 8 * sizeof(unsigned long long);
+  if (trace_env && workspace_bytes >= ((need + 255) / 256) * 256 + trace_bytes)
+    p.trace = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(workspace) + ((need + 255) / 256) * 256);
+  char *cursor = reinterpret_cast<char *>(workspace) + kChainPartialOffset;
+  int rc;
+  bool any_gemm = false;
+  for (int i = 0; i < n_ops; ++i) {
+    const eb_chain_op &o = ops[i];
+    if (o.type == EB_OP_GEMM) {
+      any_gemm = true;
+      EB_REQUIRE(o.A && o.W && o.C, "decode_chain: op %d: null GEMM operand", i);
+      EB_REQUIRE(o.N > 0 && o.K >= 8 && o.K % 8 == 0 && o.N % 8 == 0, "decode_chain: op %d: K and N must be multiples of 8", i);
+      EB_REQUIRE(o.lda >= o.K && o.ldw >= o.K && o.lda % 8 == 0 && o.ldw % 8 == 0 && o.ldc >= o.N,
+                 "decode_chain: op %d: bad leading dimensions", i);
+      EB_REQUIRE(!o.residual || (o.ldr >= o.N && o.ldr % 8 == 0), "decode_chain: op %d: bad residual stride", i);
+      EB_REQUIRE(o.out_dtype == dtype || o.out_dtype == EB_F32, "decode_chain: op %d: bad output type", i);
+      EB_REQUIRE(o.act >= EB_ACT_NONE && o.act <= EB_ACT_GELU_ERF, "decode_chain: op %d: unknown activation", i);
+      EB_REQUIRE(aligned16(o.A) && aligned16(o.W) && aligned16(o.C), "decode_chain: op %d: pointers must be 16-byte aligned", i);
+      ChainGemm &g = p.g[i];
+      p.type[i] = kOpGemm;
+      g.N = o.N; g.K = o.K;
+      g.kblocks = (o.K + kBlockK - 1) / kBlockK;
+      g.nsk = (g.kblocks + p.kpb - 1) / p.kpb;
+      g.tiles = (o.N + kLanes - 1) / kLanes;
+      const long long total = (long long)g.tiles * g.nsk;
+      EB_REQUIRE(total < (1ll << 30), "decode_chain: op %d too large", i);
+      g.units_per_cta = (int)((total + grid - 1) / grid);
+      g.C = o.C; g.ldc = o.ldc; g.c_rows_per_batch = o.c_rows_per_batch; g.c_batch_stride = o.c_batch_stride;
+      g.c_row_offset_dev = o.c_row_offset_device;
+      g.bias = o.bias; g.residual = o.residual; g.ldr = o.ldr; g.act = o.act; g.out_f32 = o.out_dtype == EB_F32;
+      EB_REQUIRE((size_t)g.tiles * sizeof(int) <= kChainTileCounterBytes, "decode_chain: op %d: N too large", i);
+      g.counters = reinterpret_cast<int *>(reinterpret_cast<char *>(workspace) + kChainHeadBytes + i * kChainTileCounterBytes);
+      g.partial = reinterpret_cast<float *>(cursor);
+      cursor += chain_op_bytes(grid, bn);
+      if ((rc = make_map(&maps.w[i], o.W, dtype, o.N, o.K, o.ldw, kLanes))) return rc;
+      if ((rc = make_map(&maps.x[i], o.A, dtype, M, o.K, o.lda, bn))) return rc;
+    } else if (o.type == EB_OP_LAYERNORM) {
+      EB_REQUIRE(o.x && o.y && o.gamma && o.beta && o.n2 > 0 && o.n2 % 8 == 0, "decode_chain: op %d: bad LayerNorm operands", i);
+      EB_REQUIRE(aligned16(o.x) && aligned16(o.y) && aligned16(o.gamma) && aligned16(o.beta),
+                 "decode_chain: op %d: pointers must be 16-byte aligned", i);
+      p.type[i] = kOpLayerNorm;
+      p.l[i] = ChainLn{o.x, o.gamma, o.beta, o.y, o.n2, (float)o.eps};
+    } else {
+      return fail(EB_EINVAL, "decode_chain: op %d: unknown type %d", i, o.type);
+    }
+  }
+  EB_REQUIRE(any_gemm, "decode_chain: a chain needs at least one GEMM");
+  cudaStream_t st = as_stream(stream);
+#define EB_CHAIN(BN) (dtype == EB_F16 ? launch_chain<__half, BN>(maps, p, grid, smem, st) \
+                                      : launch_chain<__nv_bfloat16, BN>(maps, p, grid, smem, st))
+  if (bn == 16) return EB_CHAIN(16);
+  if (bn == 32) return EB_CHAIN(32);
+  if (bn == 64) return EB_CHAIN(64);
+  return EB_CHAIN(128);
+#undef EB_CHAIN
+}
 
 extern "C" size_t eb_gemm_workspace_bytes(int M, int N, int K) {
   if (M > kLanes || M <= 0 || N <= 0 || K <= 0) return 0;

@@ -193,6 +193,42 @@ EB_API int eb_gemm_allreduce(const void *A, long long lda, const void *W, long l
                       int flag_slots_per_source, int parity, void *stream);
 EB_API size_t eb_gemm_allreduce_recv_bytes(int world, int M, int N);
 
+/* ---- a chain of generation-step operations in one launch ----------------------------------- */
+
+#define EB_OP_GEMM 0
+#define EB_OP_LAYERNORM 1
+
+/* One operation of eb_decode_chain.  GEMM: C = act(A . W^T + bias) + residual with the fields of
+ * eb_gemm (A [M,K], W [N,K], static weights).  LayerNorm: y = gamma * norm(x) + beta over M rows
+ * of n2 elements (x, y, gamma, beta in the chain's dtype). */
+typedef struct eb_chain_op {
+  int type;
+  const void *A; long long lda; const void *W; long long ldw; void *C; long long ldc;
+  const void *bias; const void *residual; long long ldr;
+  int N, K, out_dtype, act, c_rows_per_batch;
+  long long c_batch_stride;
+  const int32_t *c_row_offset_device;
+  const void *x; void *y; const void *gamma; const void *beta;
+  int n2;
+  double eps;
+} eb_chain_op;
+
+/* Runs up to 8 dependent operations (each consumes the previous one's complete output) of a
+ * generation step, M <= 128 rows, as ONE persistent kernel: e.g. the tail of a decoder layer
+ * (energonai/model/endecoder.py:48-70) out-proj -> norm2 -> FC1 -> FC2 -> next layer's norm1 ->
+ * next layer's QKV projection.  Between operations the grid synchronises through arrival
+ * counters in `workspace`, while the weights of the following GEMM keep streaming into shared
+ * memory (weights must be static: nobody may be writing them).  Results are identical to
+ * running eb_gemm / eb_layer_norm_fwd one after the other.  Buffers written by an operation
+ * must not alias anything an earlier operation of the same chain reads.  `workspace`:
+ * eb_decode_chain_workspace_bytes(...) bytes, 16-byte aligned, zero-filled once before first
+ * use; launches sharing it must not overlap on the device.  All grid-wide waits are bounded
+ * (1 s, eb_device_status).  The kernel needs every SM to host one of its CTAs at the same time:
+ * do not run it concurrently with other work that pins shared memory on the device. */
+EB_API int eb_decode_chain(const eb_chain_op *ops, int n_ops, int M, int dtype, void *workspace,
+                    size_t workspace_bytes, void *stream);
+EB_API size_t eb_decode_chain_workspace_bytes(const eb_chain_op *ops, int n_ops, int M);
+
 /* ---- fused attention ----------------------------------------------------------------------- */
 
 /* Replaces the score / mask / softmax / value products of MultiHeadAttention1D.forward
