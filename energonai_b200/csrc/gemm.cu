@@ -223,6 +223,7 @@ template <int BN, bool SWAP> struct Scheduler {
   const GemmParams &p;
   int lane_tiles, col_tiles, nsk;
   int pos, end;              // 32-bit on purpose: these feed divisions on the critical path
+  int h0, h1;                // swap mode: the CTA's last, partial tile, which it processes FIRST
   bool first;
   __device__ Scheduler(const GemmParams &pp) : p(pp) {
     lane_tiles = (p.lane_rows + kLanes - 1) / kLanes;
@@ -230,15 +231,35 @@ template <int BN, bool SWAP> struct Scheduler {
     nsk = (p.kblocks + p.kpb - 1) / p.kpb;
     first = true;
     if (SWAP) {
+      // The CTA owns the stage range [pos, end) of the tile-major sequence.  If the range ends
+      // inside a tile (and started before it), that partial piece [h0, h1) goes first, then
+      // the rest in order: partial pieces need the cross-CTA sum, whose round trips are hidden
+      // while later stages stream in, and the pieces a CTA finishes with are complete tiles.
       const int total = lane_tiles * nsk;
       pos = (int)blockIdx.x * p.units_per_cta;
       end = pos + p.units_per_cta < total ? pos + p.units_per_cta : total;
+      h0 = h1 = 0;
+      if (end > pos) {
+        const int tile_start = (end / nsk) * nsk;
+        if (end > tile_start && tile_start > pos) { h0 = tile_start; h1 = end; end = tile_start; }
+      }
     } else {
       pos = blockIdx.x;
       end = lane_tiles * col_tiles;
     }
   }
   __device__ bool next(Segment &s) {
+    if (SWAP && h1 > h0) {
+      s.lane_tile = h0 / nsk;
+      s.col_tile = 0;
+      s.sk0 = 0;
+      s.sk1 = h1 - h0;
+      s.partial = true;
+      s.which = 1;             // not the first piece of the range in k order
+      s.lane_row0 = s.lane_tile * kLanes;
+      h1 = h0;
+      return true;
+    }
     if (pos >= end) return false;
     if (SWAP) {
       s.lane_tile = pos / nsk;
@@ -546,34 +567,63 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
 #pragma unroll
           for (int m = 0; m < BN; ++m)
             if (m < p.M) __stcg(mine + (size_t)m * kLanes + lrow, v[m]);
-          __threadfence();
-          if (!epi_sync()) { alive = false; continue; }
           // CTAs whose unit range intersects this tile
           const int t0 = s.lane_tile * sched.nsk;
           const int first_cta = t0 / p.units_per_cta;
           const int last_cta = (t0 + sched.nsk - 1) / p.units_per_cta;
-          if (threadIdx.x == 64) {
-            const int arrived = atomicAdd(p.counters + s.lane_tile, 1);
-            const int is_last = arrived == last_cta - first_cta;
-            if (is_last) p.counters[s.lane_tile] = 0;      // ready for the next call
-            last_flag[flag_slot] = is_last;
-          }
-          if (!epi_sync()) { alive = false; continue; }
-          do_epilogue = last_flag[flag_slot] != 0;         // the other slot is written next time
-          flag_slot ^= 1;
-          if (do_epilogue) {
+          if (p.comm.world > 1) {
+            // the exchange below is a whole-CTA protocol: one arrival counter per tile
             __threadfence();
-#pragma unroll
-            for (int m = 0; m < BN; ++m) v[m] = 0.f;
-            // contributors are read four at a time (all their loads in flight together) and
-            // added in CTA order, so the sum does not depend on which CTA arrived last
+            if (!epi_sync()) { alive = false; continue; }
+            if (threadIdx.x == 64) {
+              const int arrived = atomicAdd(p.counters + 4 * s.lane_tile, 1);
+              const int is_last = arrived == last_cta - first_cta;
+              if (is_last) p.counters[4 * s.lane_tile] = 0;      // ready for the next call
+              last_flag[flag_slot] = is_last;
+            }
+            if (!epi_sync()) { alive = false; continue; }
+            do_epilogue = last_flag[flag_slot] != 0;         // the other slot is written next time
+            flag_slot ^= 1;
+            if (do_epilogue) __threadfence();
+          } else {
+            // Each warp owns a quarter of the tile's rows in every CTA, so the hand-over is done
+            // warp by warp (one counter per tile and quarter): no CTA-wide rendezvous, and the
+            // release / acquire ride on the counter update itself.
+            __syncwarp();
+            int arrived = 0;
+            int *counter = p.counters + 4 * s.lane_tile + quarter;
+            if (lane == 0) {
+              asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(counter) : "memory");
+              if (arrived == last_cta - first_cta) *counter = 0;   // ready for the next call
+            }
+            arrived = __shfl_sync(0xffffffffu, arrived, 0);
+            __syncwarp();
+            do_epilogue = arrived == last_cta - first_cta;
+          }
+          if (do_epilogue) {
+            // The contributions are added in CTA order, so the sum does not depend on which CTA
+            // arrived last; this CTA's own comes from its registers, the others' are read up to
+            // kBatch at a time with all their loads in flight together.
             constexpr int kBatch = BN <= 16 ? 4 : (BN <= 32 ? 2 : 1);
-            for (int c0 = first_cta; c0 <= last_cta; c0 += kBatch) {
+            // (for the widest tile the registers do not hold two accumulators: there the own
+            // contribution is read back from memory like the others)
+            constexpr bool kOwnRegs = BN <= 64;
+            const int me = kOwnRegs ? (int)blockIdx.x : -1, n_others = last_cta - first_cta + (kOwnRegs ? 0 : 1);
+            float sum_store[kOwnRegs ? BN : 1];
+            float *sum = kOwnRegs ? sum_store : v;
+            if (!kOwnRegs) {
+#pragma unroll
+              for (int m = 0; m < BN; ++m) v[m] = 0.f;
+            }
+#pragma unroll
+            for (int m = 0; m < (kOwnRegs ? BN : 1); ++m) sum_store[m] = 0.f;
+            bool own_added = !kOwnRegs;
+            for (int o0 = 0; o0 < n_others || !own_added; o0 += kBatch) {
               float t[kBatch][BN];
 #pragma unroll
               for (int j = 0; j < kBatch; ++j) {
-                const int cta = c0 + j;
-                if (cta <= last_cta) {
+                if (o0 + j < n_others) {
+                  const int cta = first_cta + o0 + j + ((kOwnRegs && first_cta + o0 + j >= me) ? 1 : 0);
                   const int which = cta * p.units_per_cta >= t0 ? 0 : 1;   // its range starts inside this tile
                   const float *theirs = p.partial + ((size_t)(cta * 2 + which) * BN) * kLanes;
 #pragma unroll
@@ -582,12 +632,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
                 }
               }
 #pragma unroll
-              for (int j = 0; j < kBatch; ++j)
-                if (c0 + j <= last_cta) {
+              for (int j = 0; j < kBatch; ++j) {
+                if (o0 + j < n_others) {
+                  const int cta = first_cta + o0 + j + ((kOwnRegs && first_cta + o0 + j >= me) ? 1 : 0);
+                  if (!own_added && cta > me) {
+#pragma unroll
+                    for (int m = 0; m < BN; ++m) sum[m] += v[m];
+                    own_added = true;
+                  }
 #pragma unroll
                   for (int m = 0; m < BN; ++m)
-                    if (m < p.M) v[m] += t[j][m];
+                    if (m < p.M) sum[m] += t[j][m];
                 }
+              }
+              if (o0 + kBatch >= n_others && !own_added) {
+#pragma unroll
+                for (int m = 0; m < BN; ++m) sum[m] += v[m];
+                own_added = true;
+              }
+            }
+            if (kOwnRegs) {
+#pragma unroll
+              for (int m = 0; m < BN; ++m) v[m] = sum[m];
             }
           }
         }
@@ -772,7 +838,7 @@ inline void swap_split(int N, int K, int kpb, int *grid, int *units) {
   *grid = (int)((total + *units - 1) / *units);
 }
 
-constexpr size_t kCounterBytes = 64 * 1024;   // workspace head: one int per 128-row tile, zero between calls
+constexpr size_t kCounterBytes = 64 * 1024;   // workspace head: four ints per 128-row tile, zero between calls
 
 #include "gemm_chain.cuh"
 
@@ -971,7 +1037,7 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
     EB_REQUIRE((long long)((N + kLanes - 1) / kLanes) * ((K + kBlockK - 1) / kBlockK) < (1ll << 30), "gemm: N*K too large");
     swap_split(N, K, p.kpb, &grid, &p.units_per_cta);
     const size_t tiles = (N + kLanes - 1) / kLanes;
-    EB_REQUIRE(tiles * sizeof(int) <= kCounterBytes, "gemm: N=%d exceeds the decode path's tile-counter capacity", N);
+    EB_REQUIRE(tiles * 4 * sizeof(int) <= kCounterBytes, "gemm: N=%d exceeds the decode path's tile-counter capacity", N);
     // The counters sit at a fixed place (the head of the workspace) so that calls of any
     // shape find them zero; the partials behind them need no initialisation.
     const size_t need = kCounterBytes + (size_t)grid * 2 * bn * kLanes * sizeof(float);

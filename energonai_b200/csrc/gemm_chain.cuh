@@ -130,6 +130,7 @@ chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ Cha
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    EB_TRACE(0, 7);
     for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
@@ -307,6 +308,7 @@ chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ Cha
           for (int sk = sk0; sk < sk1; ++sk) {
             if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, 3)) { ok = false; break; }
             tcgen05_fence_after();
+            if (c.pos == (int)blockIdx.x * g.units_per_cta && sk == sk0) EB_TRACE(op, 5);
             for (int j = 0; j < kpb && sk * kpb + j < g.kblocks; ++j) {
               const uint32_t a_addr = tiles_addr + slot * stage_bytes + j * sub_bytes;
               const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + lane_bytes);
@@ -322,6 +324,7 @@ chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ Cha
           if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
           c.pos += sk1 - sk0;
         }
+        EB_TRACE(op, 6);
       }
     }
   } else {
