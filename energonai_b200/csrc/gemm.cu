@@ -82,6 +82,15 @@ struct GemmParams {
   int kpb;                       // k-blocks (64 columns each) per pipeline stage / barrier hand-over
   int static_w;                  // W may be read before the preceding kernel of the stream has finished
   CommParams comm;
+  // swap mode, optional: the A operand is the un-normalised input of a LayerNorm whose scale
+  // was multiplied into W beforehand.  The kernel computes each row's mean / inverse std over
+  // K itself and the last epilogue of a tile evaluates
+  //   y[m][n] = rstd[m] * (acc[m][n] - mean[m] * ln_colsum[n]) + ln_bias[n]
+  // (ln_colsum[n] = sum_k W'[n][k], ln_bias[n] = bias[n] + sum_k W[n][k] * beta[k], both fp32).
+  const float *ln_colsum, *ln_bias;
+  const void *ln_x;
+  long long ln_ldx;
+  float ln_eps;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -478,6 +487,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
       epi_phase ^= 1u;
       return ok;
     };
+    // Folded LayerNorm: row statistics of the activations, computed here while the first
+    // weight stages are on their way (these warps have nothing else to do yet).  BN / 128 of
+    // the epilogue threads share a row; shifted single-pass sums as in the LayerNorm kernel.
+    constexpr bool kCanFold = SWAP && BN <= 32;
+    float *ln_mean_s = reinterpret_cast<float *>(smem + 640), *ln_rstd_s = ln_mean_s + 32;
+    const bool fold = kCanFold && p.ln_colsum != nullptr;
+    if (kCanFold && fold) {
+      constexpr int tpr = 128 / (kCanFold ? BN : 128);          // threads per row
+      const int et = threadIdx.x - 64, r = et / tpr, j = et % tpr;
+      float sum = 0.f, sq = 0.f, pivot = 0.f;
+      if (r < p.M) {
+        const T *xr = reinterpret_cast<const T *>(p.ln_x) + (long long)r * p.ln_ldx;
+        pivot = to_f32<T>(__ldcg(xr));
+        const int packs = p.K / 8;
+#pragma unroll 8
+        for (int pk = j; pk < packs; pk += tpr) {
+          Vec16<T> a;
+          a.raw = __ldcg(reinterpret_cast<const uint4 *>(xr) + pk);
+          float f[8];
+          a.unpack(f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { const float d = f[e] - pivot; sum += d; sq += d * d; }
+        }
+      }
+#pragma unroll
+      for (int o = tpr / 2; o > 0; o >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      }
+      if (j == 0) {
+        const float inv_k = 1.f / (float)p.K, ms = sum * inv_k;
+        ln_mean_s[r] = r < p.M ? pivot + ms : 0.f;
+        ln_rstd_s[r] = r < p.M ? rsqrtf(fmaxf(sq * inv_k - ms * ms, 0.f) + p.ln_eps) : 0.f;
+      }
+      if (!epi_sync()) alive = false;
+    }
     while (alive && sched.next(s)) {
       if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4)) break;
       tcgen05_fence_after();
@@ -550,7 +595,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
         // below, every load would wait for the store before it (the two may alias).
         constexpr bool kEarlyRes = BN <= 32;
         T r_early[kEarlyRes ? BN : 1];
-        const float b = (bias && n_ok) ? to_f32<T>(bias[n]) : 0.f;
+        const float b = !n_ok ? 0.f : fold ? __ldg(p.ln_bias + n) : bias ? to_f32<T>(bias[n]) : 0.f;
+        const float colsum = (fold && n_ok) ? __ldg(p.ln_colsum + n) : 0.f;
         if (kEarlyRes && res && n_ok) {
 #pragma unroll
           for (int m = 0; m < (kEarlyRes ? BN : 1); ++m)
@@ -745,7 +791,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
             for (int j = 0; j < 16; ++j) {
               const int m = m0 + j;
               if (m < p.M) {
-                float x = apply_act(v[m] + b, p.act);
+                float x = v[m];
+                if (kCanFold && fold) x = ln_rstd_s[m & 31] * (x - ln_mean_s[m & 31] * colsum);
+                x = apply_act(x + b, p.act);
                 if (res) x += to_f32<T>(kEarlyRes ? r_early[kEarlyRes ? m : 0] : r_late[j]);
                 const long long off = c_row_offset(p, m) + n;
                 if (p.out_f32) reinterpret_cast<float *>(p.C)[off] = x;
@@ -988,8 +1036,16 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
                      const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
                      int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
                      const int32_t *c_row_offset_device, int flags, void *workspace, size_t workspace_bytes,
-                     void *stream, const CommParams *comm) {
+                     void *stream, const CommParams *comm, const float *ln_colsum = nullptr,
+                     const float *ln_bias = nullptr, double ln_eps = 0.0) {
   EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "gemm: operands must be fp16 or bf16 (got dtype %d)", dtype);
+  if (ln_colsum || ln_bias) {
+    EB_REQUIRE(ln_colsum && ln_bias, "gemm_ln: ln_colsum and ln_bias go together");
+    EB_REQUIRE(M <= 32, "gemm_ln: the folded LayerNorm serves M <= 32 rows (got %d)", M);
+    EB_REQUIRE(!bias, "gemm_ln: the bias is part of ln_bias");
+    EB_REQUIRE(ln_eps > 0.0, "gemm_ln: eps must be positive");
+    EB_REQUIRE(((uintptr_t)ln_colsum % 4 == 0) && ((uintptr_t)ln_bias % 4 == 0), "gemm_ln: misaligned fp32 vectors");
+  }
   EB_REQUIRE(out_dtype == dtype || out_dtype == EB_F32, "gemm: output must be the input type or fp32");
   EB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "gemm: negative size");
   EB_REQUIRE(act >= EB_ACT_NONE && act <= EB_ACT_GELU_ERF, "gemm: unknown activation %d", act);
@@ -1011,6 +1067,7 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
   p.c_row_offset_dev = c_row_offset_device;
   p.static_w = (flags & EB_GEMM_STATIC_W) ? 1 : 0;
   if (comm) p.comm = *comm;
+  p.ln_colsum = ln_colsum; p.ln_bias = ln_bias; p.ln_x = A; p.ln_ldx = lda; p.ln_eps = (float)ln_eps;
   EB_REQUIRE(!comm || comm->world <= 1 || M <= kLanes, "gemm_allreduce: the fused exchange serves M <= 128 only (M=%d)", M);
   EB_REQUIRE(!comm || comm->world <= 1 || (long long)((N + kLanes - 1) / kLanes) <= comm->max_tiles,
              "gemm_allreduce: N=%d needs more flag slots than the exchange area has", N);
@@ -1082,6 +1139,17 @@ extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ld
                        void *stream) {
   return gemm_impl(A, lda, W, ldw, C, ldc, bias, residual, ldr, M, N, K, dtype, out_dtype, act, c_rows_per_batch,
                    c_batch_stride, c_row_offset_device, flags, workspace, workspace_bytes, stream, nullptr);
+}
+
+extern "C" int eb_gemm_ln(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
+                          const float *ln_colsum, const float *ln_bias, double eps, const void *residual,
+                          long long ldr, int M, int N, int K, int dtype, int out_dtype, int act,
+                          int c_rows_per_batch, long long c_batch_stride, const int32_t *c_row_offset_device,
+                          int flags, void *workspace, size_t workspace_bytes, void *stream) {
+  EB_REQUIRE(ln_colsum && ln_bias, "gemm_ln: ln_colsum and ln_bias are required");
+  return gemm_impl(A, lda, W, ldw, C, ldc, nullptr, residual, ldr, M, N, K, dtype, out_dtype, act, c_rows_per_batch,
+                   c_batch_stride, c_row_offset_device, flags, workspace, workspace_bytes, stream, nullptr, ln_colsum,
+                   ln_bias, eps);
 }
 
 extern "C" size_t eb_gemm_allreduce_recv_bytes(int world, int M, int N) {

@@ -20,14 +20,16 @@ def workspace(device, nbytes):
 
 
 def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out_rows_per_batch=0,
-         out_batch_stride=0, out_ld=None, out_row_offset_device=None, static_weight=False, peer=None):
+         out_batch_stride=0, out_ld=None, out_row_offset_device=None, static_weight=False, peer=None, ln_fold=None):
     """a [M,K] (row stride allowed), w [N,K]; returns out [M,N].
 
     `out`, if given, receives the result; with out_rows_per_batch > 0 row m is written at
     element (m // rpb) * out_batch_stride + (m % rpb) * out_ld of `out` (a view into a cache);
     out_row_offset_device (int32 device scalar) adds that many rows of out_ld at run time.
     static_weight=True promises that `w` is not being written by earlier work still in flight
-    on the stream (model weights), which lets the kernel prefetch it early."""
+    on the stream (model weights), which lets the kernel prefetch it early.
+    ln_fold=(colsum, bias32, eps), from fold_layernorm(): `a` is the un-normalised input of a
+    LayerNorm and `w` the weight with the LayerNorm scale folded in (M <= 32 only)."""
     require_cuda(a, w, bias, residual, out)
     if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1]:
         raise RuntimeError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T do not match")
@@ -49,6 +51,18 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
     code = ACT_CODES[act] if not isinstance(act, int) else act
     nbytes = lib().eb_gemm_workspace_bytes(M, N, K)
     ws = workspace(a.device, nbytes) if nbytes else None
+    if ln_fold is not None:
+        colsum, bias32, eps = ln_fold
+        if bias is not None or peer is not None and peer.world > 1:
+            raise RuntimeError("gemm: ln_fold carries the bias and does not combine with the peer exchange")
+        if colsum.dtype != torch.float32 or bias32.dtype != torch.float32 or colsum.numel() != N or bias32.numel() != N:
+            raise RuntimeError("gemm: ln_fold vectors must be fp32 of length N")
+        check(lib().eb_gemm_ln(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out_ld, ptr(colsum), ptr(bias32), float(eps),
+                               ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K,
+                               dtype_code(a.dtype), dtype_code(out_dtype), code, out_rows_per_batch, out_batch_stride,
+                               ptr(out_row_offset_device), 1 if static_weight else 0, ptr(ws),
+                               ws.numel() if ws is not None else 0, stream_ptr()), "gemm_ln")
+        return out
     if peer is not None and peer.world > 1:
         if not peer.fits(M, N):
             raise RuntimeError(f"gemm: {M} x {N} does not fit the peer exchange areas")
@@ -66,6 +80,25 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
                         ptr(out_row_offset_device), 1 if static_weight else 0, ptr(ws),
                         ws.numel() if ws is not None else 0, stream_ptr()), "gemm")
     return out
+
+
+LN_FOLD_MAX_ROWS = 32
+
+
+def fold_layernorm(weight, bias, gamma, beta):
+    """One-time preparation for gemm(..., ln_fold=...): y = LayerNorm(x; gamma, beta) @ weight.T + bias
+    equals rstd * (x @ w_folded.T - mean * colsum) + bias32 with
+      w_folded = weight * gamma (rounded to the weight dtype), colsum = w_folded.sum(1),
+      bias32 = bias + weight @ beta   (fp32).
+    Returns (w_folded, colsum, bias32)."""
+    with torch.no_grad():
+        w32 = weight.detach().float()
+        w_folded = (w32 * gamma.detach().float()[None, :]).to(weight.dtype).contiguous()
+        colsum = w_folded.float().sum(1).contiguous()
+        bias32 = w32 @ beta.detach().float()
+        if bias is not None:
+            bias32 = bias32 + bias.detach().float()
+        return w_folded, colsum, bias32.contiguous()
 
 
 def device_status(clear=True):

@@ -14,7 +14,7 @@ from torch import nn, dtype
 
 from ..attention import attention_prefill, attention_decode
 from ..gemm import gemm
-from ..nn import Linear1D_Col, Linear1D_Row
+from ..nn import Linear1D_Col, Linear1D_Row, FoldCache, tensor_version
 from ..tp import get_tp, divide
 
 
@@ -69,6 +69,7 @@ class MultiHeadAttention1D(nn.Module):
         self.dense = Linear1D_Row(hidden_size, hidden_size, bias=True, dtype=dtype, parallel_input=True)
         self.past_cache = KVCache()
         self._packed_w = self._packed_b = None
+        self._fold = FoldCache()
 
     # -- one [3*local_hidden, hidden] weight in k|v|q order, shared with the named parameters --
     def _packed(self):
@@ -90,14 +91,20 @@ class MultiHeadAttention1D(nn.Module):
             self._packed_w, self._packed_b = w, b
         return self._packed_w, self._packed_b
 
+    def _param_versions(self):
+        mods = (self.query_key_value,) if self.fused_qkv else (self.key_, self.value_, self.query_)
+        return tuple(tensor_version(t) for m in mods for t in (m.weight, m.bias) if t is not None)
+
     def forward(self, hidden_states, attention_mask=None, first_cache=False, seq_lens=None, residual=None,
-                kv_state=None):
+                kv_state=None, fold_norm=None):
         """hidden_states [batch, seq, hidden].  attention_mask: additive, [batch, 1, 1, kv_len]
         (0 / -10000), or None.  With a cache, first_cache=True runs the whole prompt and any
         later call appends the last position.  `residual`, if given, is added to the output
         inside the projection's epilogue (the block's skip connection).  `kv_state`, used when a
         generation step is captured in a CUDA graph, is a device int32 pair [position, length]
-        that the kernels read instead of host values; the cache must already have room."""
+        that the kernels read instead of host values; the cache must already have room.
+        `fold_norm` (generation steps only): the LayerNorm1D in front of this module;
+        hidden_states is then its un-normalised input and the QKV GEMM normalises on the fly."""
         B, S, _ = hidden_states.shape
         hl, d = self.local_hidden, self.attention_head_size
         w, b = self._packed()
@@ -122,12 +129,16 @@ class MultiHeadAttention1D(nn.Module):
         else:
             x = hidden_states[:, -1, :]
             mask = attention_mask.reshape(B, -1) if attention_mask is not None else None
+            fold = None
+            if fold_norm is not None:
+                w, colsum, bias32, eps = self._fold.get(w, b, fold_norm, self._param_versions())
+                b, fold = None, (colsum, bias32, eps)
             if kv_state is None:
                 pos = cache.len
                 cache.ensure(B, pos + 1, 3 * hl, x.dtype, x.device)
                 buf = cache.buf
                 gemm(x, w, bias=b, static_weight=True, out=buf[:, pos:], out_rows_per_batch=1, out_batch_stride=buf.stride(0),
-                     out_ld=buf.stride(1))
+                     out_ld=buf.stride(1), ln_fold=fold)
                 cache.len = kv_len = pos + 1
                 ctx = attention_decode(buf[:, :, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, kv_len, mask=mask,
                                        scale=self.scaling, q_in_cache=True)
@@ -135,7 +146,7 @@ class MultiHeadAttention1D(nn.Module):
                 buf = cache.buf
                 cap = buf.shape[1]
                 gemm(x, w, bias=b, static_weight=True, out=buf, out_rows_per_batch=1, out_batch_stride=buf.stride(0), out_ld=buf.stride(1),
-                     out_row_offset_device=kv_state[0:1])
+                     out_row_offset_device=kv_state[0:1], ln_fold=fold)
                 ctx = attention_decode(buf[:, :, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, cap, mask=mask,
                                        scale=self.scaling, q_in_cache=True, kv_len_device=kv_state[1:2])
             ctx = ctx.view(B, 1, hl)

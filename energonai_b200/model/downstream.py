@@ -4,6 +4,7 @@ import torch
 from torch import dtype, nn
 
 from ..gemm import gemm
+from ..nn import FoldCache
 
 
 class _Classifier(nn.Module):
@@ -13,9 +14,16 @@ class _Classifier(nn.Module):
         if weight is None:
             nn.init.normal_(self.weight, std=0.02)
         self.bias = nn.Parameter(torch.zeros(num_classes, dtype=dtype)) if bias else None
+        self._fold = FoldCache()
 
-    def forward(self, x):
-        y = gemm(x.reshape(-1, x.shape[-1]), self.weight, bias=self.bias, out_dtype=torch.float32, static_weight=True)
+    def forward(self, x, fold_norm=None):
+        """fold_norm: the final LayerNorm1D; x is then its un-normalised input (generation steps)."""
+        x2 = x.reshape(-1, x.shape[-1])
+        if fold_norm is not None:
+            w_f, colsum, bias32, eps = self._fold.get(self.weight, self.bias, fold_norm)
+            y = gemm(x2, w_f, out_dtype=torch.float32, static_weight=True, ln_fold=(colsum, bias32, eps))
+        else:
+            y = gemm(x2, self.weight, bias=self.bias, out_dtype=torch.float32, static_weight=True)
         return y.view(*x.shape[:-1], self.weight.shape[0])
 
 
@@ -32,5 +40,5 @@ class LMHead1D(nn.Module):
     def weight(self):
         return self.dense.weight
 
-    def forward(self, x):
-        return self.dense(x)
+    def forward(self, x, fold_norm=None):
+        return self.dense(x, fold_norm=fold_norm)

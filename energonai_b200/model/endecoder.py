@@ -2,12 +2,13 @@
 (energonai/model/endecoder.py:11-70): norm1 -> attention -> +residual -> norm2 -> MLP ->
 +residual, pre-LN or the reference's post-LN variant (residual taken after the norm).
 The residual additions run inside the epilogues of the two row-parallel GEMMs."""
+import os
 from typing import Callable
 
 import torch
 from torch import dtype, nn
 
-from ..nn import LayerNorm1D
+from ..nn import LayerNorm1D, can_fold
 from .attention import MultiHeadAttention1D
 from .mlp import MLP1D
 
@@ -29,6 +30,8 @@ class Block1D(nn.Module):
         super().__init__()
         self.apply_post_layernorm = apply_post_layernorm
         self.disable_past_cache = disable_past_cache
+        # generation steps: norm1 / norm2 are evaluated inside the QKV / FC1 GEMMs (pre-LN only)
+        self.fold_layernorm = os.environ.get("EB_LN_FOLD", "1") != "0"
         self.norm1 = LayerNorm1D(hidden_size, eps=layernorm_epsilon, dtype=dtype)
         self.attn = MultiHeadAttention1D(hidden_size=hidden_size, num_heads=num_heads, bias=bias, dtype=dtype,
                                          max_seq_len=max_seq_len, fused_qkv=fused_qkv, is_decoder=is_decoder,
@@ -44,6 +47,10 @@ class Block1D(nn.Module):
         loop does, or just the new position)."""
         if not (self.disable_past_cache or first_cache):
             hidden_states = hidden_states[:, -1:, :]
+            if not self.apply_post_layernorm and can_fold(hidden_states.shape[0], hidden_states.dtype, self.fold_layernorm):
+                hidden_states = self.attn(hidden_states, attention_mask=attention_mask, first_cache=False,
+                                          residual=hidden_states, kv_state=kv_state, fold_norm=self.norm1)
+                return self.mlp(hidden_states, first_cache=True, residual=hidden_states, fold_norm=self.norm2)
         normed = self.norm1(hidden_states)
         residual = normed if self.apply_post_layernorm else hidden_states
         hidden_states = self.attn(normed, attention_mask=attention_mask, first_cache=first_cache, residual=residual,

@@ -14,7 +14,7 @@ from typing import Callable, Optional
 import torch
 from torch import dtype, nn
 
-from ..nn import LayerNorm1D
+from ..nn import LayerNorm1D, can_fold
 from .downstream import LMHead1D
 from .embedding import Embedding1D
 from .endecoder import Block1D
@@ -154,11 +154,21 @@ class PipelineModel(nn.Module):
         hidden = self.embed.word_embeddings(st["tok"].view(-1, 1)) + self.embed.position_embeddings(pos_long).unsqueeze(0)
         for block in self.blocks:
             hidden = block(hidden_states=hidden, attention_mask=st["mask4"], first_cache=False, kv_state=st["kv_state"])
-        logits = self.head(self.norm(hidden))[:, -1, :]
+        logits = self._last_logits(hidden)
         tok = logits.argmax(-1)
         st["out_ids"].index_copy_(1, st["kv_state"][1:2].to(torch.long), tok.view(-1, 1))   # the new token's index
         st["tok"].copy_(tok)
         st["kv_state"].add_(1)
+
+    def _last_logits(self, hidden, record=None):
+        """Final norm + LM head of a generation step, hidden [batch, 1, hidden_size]."""
+        fold = len(self.blocks) > 0 and self.blocks[0].fold_layernorm
+        if record is None and can_fold(hidden.shape[0], hidden.dtype, fold):
+            return self.head(hidden, fold_norm=self.norm)[:, -1, :]
+        last_hidden = self.norm(hidden)
+        if record is not None:
+            record.setdefault("hidden", []).append(last_hidden[:, -1, :].clone())
+        return self.head(last_hidden)[:, -1, :]
 
     def _graph_state(self, batch_size, tgt_len, model_dtype, dev, ids_dtype):
         key = (batch_size, tgt_len, model_dtype, ids_dtype, tuple(b.attn.past_cache.buf.data_ptr() for b in self.blocks))
@@ -252,11 +262,9 @@ class PipelineModel(nn.Module):
                 mask4 = st["add_mask"][:, :pos].view(batch_size, 1, 1, pos)
                 for block in self.blocks:
                     hidden_states = block(hidden_states=hidden_states, attention_mask=mask4, first_cache=False)
-                last_hidden = self.norm(hidden_states)
-                logits = self.head(last_hidden)[:, -1, :]
+                logits = self._last_logits(hidden_states, record)
                 if record is not None:
                     record.setdefault("logits", []).append(logits.clone())
-                    record.setdefault("hidden", []).append(last_hidden[:, -1, :].clone())
                 tok = logits.argmax(-1) if greedy else self.generate(out_ids[:, :pos], logits, top_k=top_k, top_p=top_p,
                                                                      temperature=temperature)
                 out_ids[:, pos] = tok

@@ -13,13 +13,43 @@ Semantics (Megatron 1-D):
 import torch
 from torch import nn
 
-from .gemm import gemm
+from .gemm import gemm, fold_layernorm, LN_FOLD_MAX_ROWS
 from .kernel.cuda_native.layer_norm import layer_norm_forward
 from .tp import get_tp, divide
 
 
 def _flat(x):
     return x.reshape(-1, x.shape[-1])
+
+
+def tensor_version(t):
+    """In-place modification counter of a tensor; tensors created under inference_mode have none."""
+    try:
+        return t._version
+    except RuntimeError:
+        return -1
+
+
+class FoldCache:
+    """Keeps (w_folded, colsum, bias32) of fold_layernorm() for one (weight, LayerNorm) pair and
+    rebuilds it when any of the tensors involved was reassigned or written in place."""
+
+    def __init__(self):
+        self.key, self.val = None, None
+
+    def get(self, w, b, norm, versions=()):
+        g, be = norm.module.weight, norm.module.bias
+        key = (w.data_ptr(), tensor_version(w), None if b is None else (b.data_ptr(), tensor_version(b)), g.data_ptr(),
+               tensor_version(g), be.data_ptr(), tensor_version(be), tuple(versions))
+        if key != self.key:
+            self.val = fold_layernorm(w, b, g, be) + (norm.eps,)
+            self.key = key
+        return self.val
+
+
+def can_fold(rows, dtype, enabled=True):
+    """A LayerNorm can be folded into the projection that follows it for generation-step shapes."""
+    return enabled and rows <= LN_FOLD_MAX_ROWS and dtype in (torch.float16, torch.bfloat16)
 
 
 class Linear1D_Col(nn.Module):
@@ -31,9 +61,17 @@ class Linear1D_Col(nn.Module):
         self.weight = nn.Parameter(torch.empty(self.out_per_rank, in_features, dtype=dtype, device=device))
         self.bias = nn.Parameter(torch.zeros(self.out_per_rank, dtype=dtype, device=device)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
+        self._fold = FoldCache()
 
-    def forward(self, x, act=None):
-        y = gemm(_flat(x), self.weight, bias=self.bias, act=act, static_weight=True).view(*x.shape[:-1], self.out_per_rank)
+    def forward(self, x, act=None, fold_norm=None):
+        """fold_norm: the LayerNorm1D whose output this projection would consume; x is then that
+        LayerNorm's INPUT and the normalisation happens inside the GEMM (generation steps)."""
+        if fold_norm is not None:
+            w_f, colsum, bias32, eps = self._fold.get(self.weight, self.bias, fold_norm)
+            y = gemm(_flat(x), w_f, act=act, static_weight=True, ln_fold=(colsum, bias32, eps))
+        else:
+            y = gemm(_flat(x), self.weight, bias=self.bias, act=act, static_weight=True)
+        y = y.view(*x.shape[:-1], self.out_per_rank)
         return get_tp().all_gather_last_dim(y) if self.gather_output else y
 
 

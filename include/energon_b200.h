@@ -193,6 +193,22 @@ EB_API int eb_gemm_allreduce(const void *A, long long lda, const void *W, long l
                       int flag_slots_per_source, int parity, void *stream);
 EB_API size_t eb_gemm_allreduce_recv_bytes(int world, int M, int N);
 
+/* eb_gemm for M <= 32 rows with a LayerNorm folded in (generation steps): A holds the
+ * UN-normalised rows x [M, K] and W the weights already multiplied by the LayerNorm scale,
+ * W'[n][k] = W[n][k] * gamma[k], rounded to the operand type.  The kernel computes each row's
+ * mean and 1/sqrt(var + eps) over the K columns (fp32, as eb_layer_norm_fwd does) and evaluates
+ *   C[m][n] = act( rstd[m] * (sum_k x[m][k] W'[n][k] - mean[m] * ln_colsum[n]) + ln_bias[n] ) + residual[m][n]
+ * with ln_colsum[n] = sum_k W'[n][k] and ln_bias[n] = bias[n] + sum_k W[n][k] * beta[k], both fp32
+ * device vectors prepared once by the caller.  This is LayerNorm (energonai/model/endecoder.py:52,
+ * 63) followed by the column-parallel projection (attention.py:73-80, mlp.py:38) in one launch,
+ * without rounding the normalised activations to the operand type in between; K must be the
+ * whole normalised width.  Other arguments, workspace and errors as eb_gemm. */
+EB_API int eb_gemm_ln(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
+               const float *ln_colsum, const float *ln_bias, double eps, const void *residual, long long ldr,
+               int M, int N, int K, int dtype, int out_dtype, int act, int c_rows_per_batch,
+               long long c_batch_stride, const int32_t *c_row_offset_device, int flags, void *workspace,
+               size_t workspace_bytes, void *stream);
+
 /* ---- a chain of generation-step operations in one launch ----------------------------------- */
 
 #define EB_OP_GEMM 0

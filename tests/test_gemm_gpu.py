@@ -135,3 +135,55 @@ def test_gemm_rejects_bad_arguments():
         gemm(a, w)
     with pytest.raises(RuntimeError):
         gemm(a.float(), w.float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("act", [None, "relu"])
+@pytest.mark.parametrize("M,N,K", [(16, 5120, 5120), (1, 256, 128), (16, 1920, 5120), (32, 1024, 768), (5, 520, 200),
+                                   (16, 8, 8), (20, 2560, 1024)])
+def test_gemm_ln_fold(M, N, K, act, dtype):
+    """LayerNorm folded into the GEMM (eb_gemm_ln) against LayerNorm -> projection in fp32.
+
+    Tolerance: besides the rounding of the output, the folded weights W * gamma are rounded to
+    the operand type once more (relative 2^-11 / 2^-8 per weight, averaging out over K), while the
+    normalised activations are NOT rounded as they are on the two-kernel path; the bound is
+    twice the plain GEMM's."""
+    from energonai_b200.gemm import gemm, fold_layernorm
+    from energonai_b200.kernel.cuda_native.layer_norm import layer_norm_forward
+    g = torch.Generator(device="cuda").manual_seed(M + 3 * N + 7 * K)
+    x = (torch.randn(M, K, device="cuda", generator=g) * 2.0 + 0.7).to(dtype)
+    x[:, 0] += 6.0                                             # an outlier column, as residual streams have
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(dtype)
+    b = torch.randn(N, device="cuda", generator=g).to(dtype)
+    gamma = (1 + 0.2 * torch.randn(K, device="cuda", generator=g)).to(dtype)
+    beta = (0.2 * torch.randn(K, device="cuda", generator=g)).to(dtype)
+    r = torch.randn(M, N, device="cuda", generator=g).to(dtype)
+    eps = 1e-5
+    w_f, colsum, bias32 = fold_layernorm(w, b, gamma, beta)
+    out = gemm(x, w_f, act=act, residual=r, static_weight=True, ln_fold=(colsum, bias32, eps))
+    torch.cuda.synchronize()
+    status_ok()
+    xn = torch.nn.functional.layer_norm(x.float(), (K,), gamma.float(), beta.float(), eps)
+    ref = xn @ w.float().t() + b.float()
+    if act == "relu":
+        ref = torch.relu(ref)
+    ref = ref + r.float()
+    err = (out.float() - ref).abs()
+    bound = 2 * REL[dtype] * ref.abs() + 4e-4 * ref.abs().max().clamp_min(1e-3) + 2 * REL[dtype] * (xn.abs() @ w.float().abs().t()) / K ** 0.5
+    assert not (err > bound).any(), f"max err {err.max().item():.4g} (ref max {ref.abs().max().item():.4g})"
+    # and against the two-kernel path, which rounds the normalised activations
+    two = gemm(layer_norm_forward(x, gamma, beta, eps), w, bias=b, act=act, residual=r)
+    tol = {torch.float16: 4e-3, torch.bfloat16: 3e-2}[dtype]
+    row_err = (out.float() - two.float()).abs().amax(-1)
+    assert (row_err <= tol * two.float().abs().amax(-1).clamp_min(1e-3)).all(), row_err.max().item()
+    assert torch.equal(out, gemm(x, w_f, act=act, residual=r, static_weight=True, ln_fold=(colsum, bias32, eps)))
+
+
+def test_gemm_ln_fold_rejects_wide_batches():
+    from energonai_b200.gemm import gemm, fold_layernorm
+    x = torch.zeros(33, 64, device="cuda", dtype=torch.float16)
+    w = torch.zeros(64, 64, device="cuda", dtype=torch.float16)
+    ones = torch.ones(64, device="cuda", dtype=torch.float16)
+    w_f, colsum, bias32 = fold_layernorm(w, None, ones, ones)
+    with pytest.raises(RuntimeError):
+        gemm(x, w_f, ln_fold=(colsum, bias32, 1e-5))
