@@ -23,6 +23,19 @@ def gemm_decode():
             y = gemm(x, w, static_weight=True)
         torch.cuda.synchronize()
         print("gemm_decode", M, N, K, float((y.float() - x.float() @ w.float().t()).abs().max()))
+    # the same QKV shape with the LayerNorm in front of it folded in (eb_gemm_ln)
+    from .gemm import fold_layernorm
+    N, K = 3 * h, h
+    w = torch.randn(N, K, device="cuda", dtype=torch.float16) * 0.02
+    x = torch.randn(M, K, device="cuda", dtype=torch.float16)
+    gamma = torch.ones(K, device="cuda", dtype=torch.float16)
+    beta = torch.zeros(K, device="cuda", dtype=torch.float16)
+    w_f, colsum, bias32 = fold_layernorm(w, None, gamma, beta)
+    for _ in range(2):
+        y = gemm(x, w_f, static_weight=True, ln_fold=(colsum, bias32, 1e-5))
+    torch.cuda.synchronize()
+    ref = torch.nn.functional.layer_norm(x.float(), (K,)) @ w.float().t()
+    print("gemm_decode ln_fold", M, N, K, float((y.float() - ref).abs().max()))
 
 
 def gemm_prefill():
