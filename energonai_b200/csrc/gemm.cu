@@ -881,6 +881,16 @@ inline void swap_split(int N, int K, int kpb, int *grid, int *units) {
   const long long nsk = (kblocks + kpb - 1) / kpb;
   const long long total = tiles * nsk;
   long long g = sm_count();
+  // A short K (few stages per tile, the row-parallel GEMMs of a wide tensor-parallel group) is
+  // not worth cutting: one CTA streams a whole tile in a few microseconds, which is less than
+  // the partial-sum hand-over of a shared tile costs.
+  static const int nosplit_env = getenv("EB_NOSPLIT_NSK") ? atoi(getenv("EB_NOSPLIT_NSK")) : -1;
+  const long long nosplit_nsk = nosplit_env >= 0 ? nosplit_env : 10;
+  if (nsk <= nosplit_nsk && tiles <= g) {
+    *units = (int)nsk;
+    *grid = (int)tiles;
+    return;
+  }
   if (g > total / 2) g = total / 2 > 0 ? total / 2 : 1;   // at least two stages per CTA
   *units = (int)((total + g - 1) / g);
   *grid = (int)((total + *units - 1) / *units);

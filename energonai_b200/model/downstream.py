@@ -1,5 +1,6 @@
 """LMHead1D with the reference's interface (energonai/model/downstream.py:5-26): a bias-free
-(by default) projection to the vocabulary on the tcgen05 GEMM, logits in fp32."""
+(by default) projection to the vocabulary on the tcgen05 GEMM, logits in fp32; with
+vocab_parallel every rank computes its slice of the vocabulary and the slices are gathered."""
 import torch
 from torch import dtype, nn
 
@@ -31,10 +32,12 @@ class LMHead1D(nn.Module):
     def __init__(self, hidden_size: int, vocab_size: int, word_embedding_weight: nn.Parameter = None,
                  bias: bool = False, dtype: dtype = None, vocab_parallel: bool = False) -> None:
         super().__init__()
-        if vocab_parallel:
-            raise RuntimeError("vocab-parallel LM head is not implemented (replicated head only)")
         self.vocab_parallel = vocab_parallel
-        self.dense = _Classifier(hidden_size, vocab_size, word_embedding_weight, bias=bias, dtype=dtype)
+        if vocab_parallel:
+            from ..nn import VocabParallelClassifier1D
+            self.dense = VocabParallelClassifier1D(hidden_size, vocab_size, bias=bias, dtype=dtype, gather_output=True)
+        else:
+            self.dense = _Classifier(hidden_size, vocab_size, word_embedding_weight, bias=bias, dtype=dtype)
 
     @property
     def weight(self):

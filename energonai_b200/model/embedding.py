@@ -12,8 +12,10 @@ class Embedding1D(nn.Module):
                  padding_idx: int = 0, dtype: dtype = None, vocab_parallel: bool = False) -> None:
         super().__init__()
         if vocab_parallel:
-            raise RuntimeError("vocab-parallel embedding is not implemented (replicated embedding only)")
-        self.word_embeddings = Embedding(vocab_size, hidden_size, padding_idx=padding_idx).to(dtype=dtype)
+            from ..nn import VocabParallelEmbedding1D
+            self.word_embeddings = VocabParallelEmbedding1D(vocab_size, hidden_size, padding_idx=padding_idx, dtype=dtype)
+        else:
+            self.word_embeddings = Embedding(vocab_size, hidden_size, padding_idx=padding_idx).to(dtype=dtype)
         self.position_embeddings = Embedding(max_seq_len, hidden_size).to(dtype=dtype)
         self.tokentype_embeddings = Embedding(num_tokentypes, hidden_size).to(dtype=dtype) if num_tokentypes > 0 else None
 

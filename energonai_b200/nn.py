@@ -103,6 +103,58 @@ class Linear1D_Row(nn.Module):
         return y.view(*x.shape[:-1], self.out_features)
 
 
+class VocabParallelEmbedding1D(nn.Module):
+    """Word embedding with the vocabulary split over the tensor-parallel ranks (the colossalai
+    layer the reference uses at energonai/model/embedding.py:21-23): rank r holds rows
+    [r * V/t, (r+1) * V/t); ids owned by another rank contribute zero and the lookups are
+    summed with one all-reduce."""
+
+    def __init__(self, num_embeddings, embedding_dim, padding_idx=None, dtype=None, device=None):
+        super().__init__()
+        tp = get_tp()
+        self.num_embeddings, self.embedding_dim, self.padding_idx = num_embeddings, embedding_dim, padding_idx
+        self.per_rank = divide(num_embeddings, tp.world_size)
+        self.vocab_start = tp.rank * self.per_rank
+        self.weight = nn.Parameter(torch.empty(self.per_rank, embedding_dim, dtype=dtype, device=device))
+        nn.init.normal_(self.weight, std=0.02)
+        if padding_idx is not None and self.vocab_start <= padding_idx < self.vocab_start + self.per_rank:
+            with torch.no_grad():
+                self.weight[padding_idx - self.vocab_start].zero_()
+
+    def forward(self, ids):
+        local = ids - self.vocab_start
+        foreign = (local < 0) | (local >= self.per_rank)
+        out = nn.functional.embedding(local.masked_fill(foreign, 0), self.weight)
+        out = out.masked_fill(foreign.unsqueeze(-1), 0)
+        return get_tp().all_reduce(out)
+
+
+class VocabParallelClassifier1D(nn.Module):
+    """Projection to a vocabulary split over the ranks (energonai/model/downstream.py:16): rank r
+    computes the logits of its V/t classes; gather_output concatenates them on the last
+    dimension in rank order."""
+
+    def __init__(self, in_features, num_classes, bias=False, dtype=None, gather_output=True, device=None):
+        super().__init__()
+        tp = get_tp()
+        self.in_features, self.num_classes, self.gather_output = in_features, num_classes, gather_output
+        self.per_rank = divide(num_classes, tp.world_size)
+        self.weight = nn.Parameter(torch.empty(self.per_rank, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(self.per_rank, dtype=dtype, device=device)) if bias else None
+        nn.init.normal_(self.weight, std=0.02)
+        self._fold = FoldCache()
+
+    def forward(self, x, fold_norm=None):
+        x2 = _flat(x)
+        if fold_norm is not None:
+            w_f, colsum, bias32, eps = self._fold.get(self.weight, self.bias, fold_norm)
+            y = gemm(x2, w_f, out_dtype=torch.float32, static_weight=True, ln_fold=(colsum, bias32, eps))
+        else:
+            y = gemm(x2, self.weight, bias=self.bias, out_dtype=torch.float32, static_weight=True)
+        y = y.view(*x.shape[:-1], self.per_rank)
+        return get_tp().all_gather_last_dim(y) if self.gather_output else y
+
+
 class _LayerNormParams(nn.Module):
     def __init__(self, n, dtype, device):
         super().__init__()

@@ -38,11 +38,17 @@ def shard_block_state(full, rank, world):
     return {k: v.contiguous() for k, v in out.items()}
 
 
-def shard_model_state(full, rank, world):
-    """State dict of a whole PipelineModel (embedding, head and final norm replicated)."""
+def shard_model_state(full, rank, world, vocab_parallel=False):
+    """State dict of a whole PipelineModel: blocks cut as above, final norm and position
+    embeddings replicated; word embedding and LM head replicated, or with vocab_parallel cut
+    into `world` row slices of the vocabulary."""
     blocks, rest = {}, {}
     for k, v in full.items():
         (blocks if k.startswith("blocks.") else rest)[k] = v
     out = dict(rest)
+    if vocab_parallel:
+        for k in ("embed.word_embeddings.weight", "head.dense.weight", "head.dense.bias"):
+            if k in out:
+                out[k] = _rows(out[k], rank, world).contiguous()
     out.update(shard_block_state(blocks, rank, world))
     return out

@@ -80,3 +80,41 @@ def test_default_context_is_single_rank():
     assert ctx.world_size == 1 and ctx.all_reduce(t) is t
     with pytest.raises(ValueError):
         tpmod.divide(10, 4)
+
+
+def _vocab_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from energonai_b200 import tp as tpmod
+        from energonai_b200.nn import VocabParallelEmbedding1D
+        from energonai_b200.sharding import shard_model_state
+        ctx = tpmod.init_tp(world)
+        V, h = 64, 16
+        gen = torch.Generator().manual_seed(8)
+        full = {"embed.word_embeddings.weight": torch.randn(V, h, generator=gen),
+                "embed.position_embeddings.weight": torch.randn(10, h, generator=gen),
+                "head.dense.weight": torch.randn(V, h, generator=gen), "norm.module.weight": torch.ones(h)}
+        shard = shard_model_state(full, rank, world, vocab_parallel=True)
+        ok = shard["embed.word_embeddings.weight"].shape == (V // world, h) and shard["head.dense.weight"].shape == (V // world, h)
+        ok = ok and shard["embed.position_embeddings.weight"].shape == (10, h)
+        emb = VocabParallelEmbedding1D(V, h, padding_idx=0)
+        with torch.no_grad():
+            emb.weight.copy_(shard["embed.word_embeddings.weight"])
+        ids = torch.randint(0, V, (3, 7), generator=gen)
+        ok = ok and torch.equal(emb(ids), F.embedding(ids, full["embed.word_embeddings.weight"]))
+        x = torch.randn(3, h, generator=gen)
+        logits = ctx.all_gather_last_dim(F.linear(x, shard["head.dense.weight"]))
+        ok = ok and torch.allclose(logits, F.linear(x, full["head.dense.weight"]), atol=1e-6)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocab_parallel_embedding_and_head_shards():
+    """Vocabulary split over two ranks: masked local lookups summed by the all-reduce equal the
+    full lookup, and the gathered per-rank logits equal the full projection."""
+    world, port = 2, _free_port()
+    ret = mp.Manager().dict()
+    mp.spawn(_vocab_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert all(ret.get(r) for r in range(world)), dict(ret)

@@ -83,3 +83,57 @@ def test_two_gpu_block_matches_oracle(use_peer):
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, port, ret, use_peer), nprocs=world, join=True)
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def _model_worker(rank, world, port, ret):
+    """A small OPT-shaped PipelineModel with vocab-parallel embedding and LM head on `world` GPUs
+    against the same weights run on one rank."""
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from energonai_b200 import tp
+        from energonai_b200.model import PipelineModel
+        from energonai_b200.sharding import shard_model_state
+        kw = dict(vocab_size=1024, max_seq_len=128, hidden_size=256, num_heads=4, depth=2, mlp_ratio=4.0,
+                  activation=torch.nn.functional.relu, dtype=torch.float16, fused_qkv=False, model_name="opt")
+        tp.set_tp(None)                                      # single-rank context: the full model
+        torch.manual_seed(21)
+        full = PipelineModel(**kw).cuda().eval()
+        with torch.no_grad():                               # livelier LayerNorms than the initial 1 / 0
+            for name, p in full.named_parameters():
+                if ".module." in name:
+                    p.add_(0.1 * torch.randn_like(p))
+        ids = torch.randint(3, 1024, (3, 11), device="cuda", generator=torch.Generator(device="cuda").manual_seed(4))
+        mask = torch.ones_like(ids)
+        mask[1, :4] = 0
+        record = {}
+        want = full(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1, record=record)
+        tp.init_tp(world)
+        model = PipelineModel(vocab_parallel=True, **kw).cuda().eval()
+        model.load_state_dict(shard_model_state(full.state_dict(), rank, world, vocab_parallel=True))
+        assert model.embed.word_embeddings.weight.shape[0] == 1024 // world
+        record_tp = {}
+        got = model(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1, record=record_tp)
+        # prompt-pass logits: the same numbers up to the all-reduce's summation order
+        a, b = record_tp["logits"][0].float(), record["logits"][0].float()
+        ok = bool(((a - b).abs() <= 2e-2 * b.abs().max()).all())
+        first = slice(11, 15)
+        ok = ok and got.shape == want.shape and float((got[:, first] == want[:, first]).float().mean()) >= 0.9
+        # all ranks hold the same tokens
+        gathered = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(gathered, got.contiguous())
+        ok = ok and all(torch.equal(gathered[0], t) for t in gathered)
+        ret[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_vocab_parallel_model():
+    import torch.multiprocessing as mp
+    world, port = 2, _free_port()
+    ret = mp.Manager().dict()
+    mp.spawn(_model_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert all(ret.get(r) for r in range(world)), dict(ret)
