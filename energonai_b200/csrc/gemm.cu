@@ -340,6 +340,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    // the descriptors are fetched now, not by the first copy that needs them
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_lane) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_col) : "memory");
     for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
@@ -524,6 +527,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
       if (!epi_sync()) alive = false;
     }
     while (alive && sched.next(s)) {
+      // Swapped orientation: the bias and the residual of this thread's outputs are requested
+      // now, all rows at once, so that their latency passes while the tile is still being
+      // multiplied; fetched inside the store loop at the end, every load would wait for the
+      // store before it (the two may alias), 15 us per launch with a residual.
+      constexpr bool kEarlyRes = SWAP && BN <= 32;
+      T r_early[kEarlyRes ? BN : 1];
+      float b = 0.f, colsum = 0.f;
+      if (SWAP) {
+        const int n = s.lane_row0 + lrow;
+        if (n < p.N) {
+          b = fold ? __ldg(p.ln_bias + n) : bias ? to_f32<T>(bias[n]) : 0.f;
+          colsum = fold ? __ldg(p.ln_colsum + n) : 0.f;
+          if (kEarlyRes && res) {
+#pragma unroll
+            for (int m = 0; m < (kEarlyRes ? BN : 1); ++m)
+              if (m < p.M) r_early[m] = __ldcg(res + (long long)m * p.ldr + n);
+          }
+        }
+      }
       if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4)) break;
       tcgen05_fence_after();
       const uint32_t t_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -590,18 +612,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
         float v[BN];
 #pragma unroll
         for (int c = 0; c < BN / 16; ++c) tmem_ld16(t_base + c * 16, v + c * 16);
-        // The residual of this thread's outputs is requested now, all rows at once, so that its
-        // DRAM latency passes during the partial-sum exchange; fetched inside the store loop
-        // below, every load would wait for the store before it (the two may alias).
-        constexpr bool kEarlyRes = BN <= 32;
-        T r_early[kEarlyRes ? BN : 1];
-        const float b = !n_ok ? 0.f : fold ? __ldg(p.ln_bias + n) : bias ? to_f32<T>(bias[n]) : 0.f;
-        const float colsum = (fold && n_ok) ? __ldg(p.ln_colsum + n) : 0.f;
-        if (kEarlyRes && res && n_ok) {
-#pragma unroll
-          for (int m = 0; m < (kEarlyRes ? BN : 1); ++m)
-            if (m < p.M) r_early[m] = __ldcg(res + (long long)m * p.ldr + n);
-        }
         // the accumulator is in registers: release it before any global traffic
         tcgen05_fence_before();
         __syncwarp();
