@@ -534,6 +534,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
       constexpr bool kEarlyRes = SWAP && BN <= 32;
       T r_early[kEarlyRes ? BN : 1];
       float b = 0.f, colsum = 0.f;
+      // run-time row offset of C (the cache row of a generation step): one load, up front
+      const long long c_extra = (SWAP && p.c_row_offset_dev) ? (long long)__ldg(p.c_row_offset_dev) * p.ldc : 0;
       if (SWAP) {
         const int n = s.lane_row0 + lrow;
         if (n < p.N) {
@@ -805,7 +807,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
                 if (kCanFold && fold) x = ln_rstd_s[m & 31] * (x - ln_mean_s[m & 31] * colsum);
                 x = apply_act(x + b, p.act);
                 if (res) x += to_f32<T>(kEarlyRes ? r_early[kEarlyRes ? m : 0] : r_late[j]);
-                const long long off = c_row_offset(p, m) + n;
+                const long long off = (p.c_rows_per_batch <= 0
+                                           ? (long long)m * p.ldc
+                                           : (long long)(m / p.c_rows_per_batch) * p.c_batch_stride +
+                                                 (long long)(m % p.c_rows_per_batch) * p.ldc) + c_extra + n;
                 if (p.out_f32) reinterpret_cast<float *>(p.C)[off] = x;
                 else reinterpret_cast<T *>(p.C)[off] = from_f32<T>(x);
               }
