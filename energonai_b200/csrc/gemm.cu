@@ -548,6 +548,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           }
         }
       }
+      if (kEarlyRes && !res) {                 // always defined: the epilogue adds it unconditionally
+#pragma unroll
+        for (int m = 0; m < (kEarlyRes ? BN : 1); ++m) r_early[m] = from_f32<T>(0.f);
+      }
       if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4)) break;
       tcgen05_fence_after();
       const uint32_t t_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -791,28 +795,71 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           }
         }
         if (do_epilogue && n_ok) {
+          // offset of row m of C, advanced row by row (a division per row by the run-time
+          // rows-per-batch cost 0.1 us each: 2 us per tile)
+          long long row_off = c_extra + n;
+          const int rpb = p.c_rows_per_batch;
+          const long long batch_step = rpb > 0 ? p.c_batch_stride - (long long)(rpb - 1) * p.ldc : p.ldc;
+          int row_in_batch = 0;
+          // Straight-line code, 16 rows at a time: all values, the activation chosen once per
+          // chunk, the residual, then all stores.  With a single warp per scheduler nothing
+          // hides a branch, and a handful of branches per row was a third of a short launch.
+          const int rows = p.M;
+          const long long ldc = p.ldc;
+          const int act = p.act;
+          const bool out_f32 = p.out_f32 != 0;
 #pragma unroll
           for (int m0 = 0; m0 < BN; m0 += 16) {
-            T r_late[16];
-            if (!kEarlyRes && res) {               // 16 rows of residual in flight together
+            float r[16];
+            if (kEarlyRes) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (m0 + j < p.M) r_late[j] = __ldcg(res + (long long)(m0 + j) * p.ldr + n);
+              for (int j = 0; j < 16; ++j) r[j] = to_f32<T>(r_early[kEarlyRes ? m0 + j : 0]);
+            } else {
+              T r_late[16];                          // 16 rows of residual in flight together
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r_late[j] = from_f32<T>(0.f);
+              if (res) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  if (m0 + j < rows) r_late[j] = __ldcg(res + (long long)(m0 + j) * p.ldr + n);
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = to_f32<T>(r_late[j]);
             }
+            float y[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int m = m0 + j;
-              if (m < p.M) {
-                float x = v[m];
-                if (kCanFold && fold) x = ln_rstd_s[m & 31] * (x - ln_mean_s[m & 31] * colsum);
-                x = apply_act(x + b, p.act);
-                if (res) x += to_f32<T>(kEarlyRes ? r_early[kEarlyRes ? m : 0] : r_late[j]);
-                const long long off = (p.c_rows_per_batch <= 0
-                                           ? (long long)m * p.ldc
-                                           : (long long)(m / p.c_rows_per_batch) * p.c_batch_stride +
-                                                 (long long)(m % p.c_rows_per_batch) * p.ldc) + c_extra + n;
-                if (p.out_f32) reinterpret_cast<float *>(p.C)[off] = x;
-                else reinterpret_cast<T *>(p.C)[off] = from_f32<T>(x);
+              const float rs = (kCanFold && fold) ? ln_rstd_s[m & 31] : 1.f;
+              const float mc = (kCanFold && fold) ? ln_mean_s[m & 31] * colsum : 0.f;
+              y[j] = rs * (v[m] - mc) + b;
+            }
+            if (act == EB_ACT_RELU) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) y[j] = fmaxf(y[j], 0.f);
+            } else if (act != EB_ACT_NONE) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) y[j] = apply_act(y[j], act);
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) y[j] += r[j];
+            if (out_f32) {
+              float *c = reinterpret_cast<float *>(p.C);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (m0 + j < rows) c[row_off] = y[j];
+                const bool wrap = ++row_in_batch == rpb;
+                row_in_batch = wrap ? 0 : row_in_batch;
+                row_off += wrap ? batch_step : ldc;
+              }
+            } else {
+              T *c = reinterpret_cast<T *>(p.C);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (m0 + j < rows) c[row_off] = from_f32<T>(y[j]);
+                const bool wrap = ++row_in_batch == rpb;
+                row_in_batch = wrap ? 0 : row_in_batch;
+                row_off += wrap ? batch_step : ldc;
               }
             }
           }
