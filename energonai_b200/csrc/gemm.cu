@@ -557,52 +557,76 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
       const uint32_t t_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
 
       if (!SWAP) {
+        // One output row per thread, 16 columns at a time.  The bias and residual of a chunk are
+        // requested two chunks ahead (their L2 latency was exposed once per chunk, which made a
+        // tile's epilogue as long as its main loop), absent operands are zeros, and the
+        // activation is chosen once per chunk: these warps are alone on their schedulers.
         const int m = s.lane_row0 + lrow;
         const bool m_ok = m < p.M;
         const long long c_off = m_ok ? c_row_offset(p, m) : 0;
+        const int n_base = s.col_tile * BN;
+        const int act = p.act;
+        const bool out_f32 = p.out_f32 != 0;
+        const T *res_row = (res && m_ok) ? res + (long long)m * p.ldr : nullptr;
+        constexpr int kChunks = BN / 16;
+        Vec16<T> bq[4][2], rq[4][2];
+        auto fetch = [&](int c, int slot) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int n = n_base + c * 16 + h * 8;
+            bq[slot][h].raw = make_uint4(0u, 0u, 0u, 0u);
+            rq[slot][h].raw = make_uint4(0u, 0u, 0u, 0u);
+            if (n < p.N) {
+              if (bias) bq[slot][h].load(bias + n);
+              if (res_row) rq[slot][h].load(res_row + n);
+            }
+          }
+        };
+        fetch(0, 0);
+        if (kChunks > 1) fetch(1, 1);
 #pragma unroll 1
-        for (int c = 0; c < BN / 16; ++c) {
-          const int n0 = s.col_tile * BN + c * 16;
-          if (n0 >= p.N) break;                     // warp-uniform
-          float v[16];
-          tmem_ld16(t_base + c * 16, v);
-          if (m_ok) {
+        for (int c4 = 0; c4 < kChunks; c4 += 4) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {           // two groups of 8 columns (N is a multiple of 8)
-              const int n = n0 + h * 8;
-              if (n < p.N) {
-                float *vv = v + h * 8;
-                if (bias) {
-                  Vec16<T> b;
-                  b.load(bias + n);
-                  float bf[8];
-                  b.unpack(bf);
+          for (int i = 0; i < 4; ++i) {
+            const int c = c4 + i;
+            const int n0 = n_base + c * 16;
+            if (c < kChunks && n0 < p.N) {            // warp-uniform
+              if (c + 2 < kChunks) fetch(c + 2, (i + 2) & 3);
+              float v[16];
+              tmem_ld16(t_base + c * 16, v);
+              if (m_ok) {
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) vv[j] += bf[j];
-                }
-                if (p.act != EB_ACT_NONE) {
+                for (int h = 0; h < 2; ++h) {         // two groups of 8 columns (N is a multiple of 8)
+                  const int n = n0 + h * 8;
+                  if (n < p.N) {
+                    float *vv = v + h * 8;
+                    float bf[8], rf[8];
+                    bq[i][h].unpack(bf);
+                    rq[i][h].unpack(rf);
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) vv[j] = apply_act(vv[j], p.act);
-                }
-                if (res) {
-                  Vec16<T> r;
-                  r.load(res + (long long)m * p.ldr + n);
-                  float rf[8];
-                  r.unpack(rf);
+                    for (int j = 0; j < 8; ++j) vv[j] += bf[j];
+                    if (act == EB_ACT_RELU) {
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) vv[j] += rf[j];
-                }
-                if (p.out_f32) {
-                  float4 *o = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.C) + c_off + n);
-                  o[0] = make_float4(vv[0], vv[1], vv[2], vv[3]);
-                  o[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
-                } else {
-                  Vec16<T> o;
-                  float tmp[8];
+                      for (int j = 0; j < 8; ++j) vv[j] = fmaxf(vv[j], 0.f);
+                    } else if (act != EB_ACT_NONE) {
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) tmp[j] = vv[j];
-                  o.pack(tmp);
-                  o.store(reinterpret_cast<T *>(p.C) + c_off + n);
+                      for (int j = 0; j < 8; ++j) vv[j] = apply_act(vv[j], act);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) vv[j] += rf[j];
+                    if (out_f32) {
+                      float4 *o = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.C) + c_off + n);
+                      o[0] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+                      o[1] = make_float4(vv[4], vv[5], vv[6], vv[7]);
+                    } else {
+                      Vec16<T> o;
+                      float tmp[8];
+#pragma unroll
+                      for (int j = 0; j < 8; ++j) tmp[j] = vv[j];
+                      o.pack(tmp);
+                      o.store(reinterpret_cast<T *>(p.C) + c_off + n);
+                    }
+                  }
                 }
               }
             }
