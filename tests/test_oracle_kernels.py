@@ -97,3 +97,28 @@ def test_linear():
     x = rng.standard_normal((2, 3, 16)).astype(np.float16)
     w = rng.standard_normal((8, 16)).astype(np.float16)
     assert np.allclose(K.linear(x, w).astype(np.float32), x.astype(np.float32) @ w.astype(np.float32).T, atol=2e-2)
+
+
+def test_fold_layernorm_identity():
+    """Host-side preparation of eb_gemm_ln: LayerNorm(x) W^T + b equals
+    rstd * (x W'^T - mean * colsum) + bias32 with the folded operands (checked in fp64 so that only
+    the algebra is tested, not rounding)."""
+    import torch
+    from energonai_b200.gemm import fold_layernorm
+    g = torch.Generator().manual_seed(12)
+    M, N, K, eps = 5, 24, 64, 1e-5
+    x = torch.randn(M, K, generator=g, dtype=torch.float64) * 3 + 1.5
+    w = torch.randn(N, K, generator=g, dtype=torch.float64)
+    b = torch.randn(N, generator=g, dtype=torch.float64)
+    gamma = 1 + 0.3 * torch.randn(K, generator=g, dtype=torch.float64)
+    beta = 0.3 * torch.randn(K, generator=g, dtype=torch.float64)
+    w_f, colsum, bias32 = fold_layernorm(w, b, gamma, beta)
+    assert w_f.dtype == w.dtype and colsum.dtype == torch.float32 and bias32.dtype == torch.float32
+    mean = x.mean(1, keepdim=True)
+    rstd = (x.var(1, unbiased=False, keepdim=True) + eps).rsqrt()
+    got = rstd * (x @ w_f.t() - mean * colsum.double()) + bias32.double()
+    want = torch.nn.functional.layer_norm(x, (K,), gamma, beta, eps) @ w.t() + b
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-5), (got - want).abs().max()
+    # without a projection bias
+    _, _, bias_only = fold_layernorm(w, None, gamma, beta)
+    assert torch.allclose(bias_only.double(), w @ beta, atol=1e-5)
