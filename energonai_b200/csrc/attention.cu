@@ -109,6 +109,29 @@ __device__ __forceinline__ void load_tile(uint32_t tile, const T *base, long lon
   }
 }
 
+// The 16 rows [warp*16, warp*16+16) of a tile, loaded by that warp alone: the generation-step
+// kernel gives every warp its own slice of each tile, so the warps need no CTA-wide barrier
+// inside the key loop.  Lane l moves chunk l % (D/8) of rows l / (D/8) + k * (32 / (D/8)).
+template <typename T, int D>
+__device__ __forceinline__ void load_warp_rows(uint32_t tile, const T *base, long long rs, int row0, int row_end,
+                                               int warp, int lane) {
+  constexpr int kChunks = D / 8, kRowStep = 32 / kChunks, kIters = 16 / kRowStep;
+  const int c = lane % kChunks, rl = lane / kChunks;
+  int row = row0 + warp * 16 + rl;
+  const T *src = base + (long long)row * rs + c * 8;
+  const long long src_step = (long long)kRowStep * rs;
+  const uint32_t dst0 = tile + (uint32_t)((warp * 16 + rl) * D * 2);
+#pragma unroll
+  for (int k = 0; k < kIters; ++k) {
+    const bool ok = row < row_end;
+    // swizzle term of row warp*16 + rl + k*kRowStep (warp*16 is a multiple of 8)
+    const uint32_t dst = dst0 + (uint32_t)(k * kRowStep * D * 2) + (uint32_t)((c ^ ((rl + k * kRowStep) & 7)) << 4);
+    cp_async16(dst, ok ? src : base, ok);
+    src += src_step;
+    row += kRowStep;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // prefill
 // ------------------------------------------------------------------------------------------------
@@ -300,12 +323,13 @@ attention_decode_kernel(const AttnParams p) {
   const T *vb = reinterpret_cast<const T *>(p.v) + b * p.v_bs + h * D;
   const T *mb = p.mask ? reinterpret_cast<const T *>(p.mask) + b * p.mask_bs : nullptr;
 
+  // every warp loads, waits for and consumes only its own 16 keys of each tile
   auto load_kv = [&](int n, int buf) {
-    load_tile<T, D>(k_s + buf * kTileBytes, kb, p.k_rs, n * kBN, Sk);
-    load_tile<T, D>(v_s + buf * kTileBytes, vb, p.v_rs, n * kBN, Sk);
-    if (threadIdx.x < kBN) {
-      const int j = n * kBN + threadIdx.x;
-      mask_s[buf * kBN + threadIdx.x] = (mb && j < Sk) ? to_f32<T>(mb[j]) * kLog2e : 0.f;
+    load_warp_rows<T, D>(k_s + buf * kTileBytes, kb, p.k_rs, n * kBN, Sk, warp, lane);
+    load_warp_rows<T, D>(v_s + buf * kTileBytes, vb, p.v_rs, n * kBN, Sk, warp, lane);
+    if (lane < 16) {
+      const int jl = warp * 16 + lane, j = n * kBN + jl;
+      mask_s[buf * kBN + jl] = (mb && j < Sk) ? to_f32<T>(mb[j]) * kLog2e : 0.f;
     }
   };
   for (int i = 0; i < kDecodeStages - 1; ++i) {
@@ -334,7 +358,7 @@ attention_decode_kernel(const AttnParams p) {
     if (n + kDecodeStages - 1 < tile1) load_kv(n + kDecodeStages - 1, (buf + kDecodeStages - 1) % kDecodeStages);
     cp_async_commit();
     cp_async_wait<kDecodeStages - 1>();
-    __syncthreads();
+    __syncwarp();
     const uint32_t kt = k_s + buf * kTileBytes, vt = v_s + buf * kTileBytes;
     // this warp's 16 keys of the tile: two 8-key n-tiles
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -385,7 +409,7 @@ attention_decode_kernel(const AttnParams p) {
       mma16816<T>(o[2 * db], pf, vf[0], vf[1]);
       mma16816<T>(o[2 * db + 1], pf, vf[2], vf[3]);
     }
-    __syncthreads();
+    __syncwarp();                // the buffer is refilled by this warp's next request
   }
   cp_async_wait<0>();
 
