@@ -552,6 +552,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
 #pragma unroll
         for (int m = 0; m < (kEarlyRes ? BN : 1); ++m) r_early[m] = from_f32<T>(0.f);
       }
+      // CTAs whose unit range intersects this tile (two divisions: done while the tile is still
+      // being multiplied, not between the accumulator and the hand-over)
+      int t0 = 0, first_cta = 0, last_cta = 0;
+      if (SWAP && s.partial) {
+        t0 = s.lane_tile * sched.nsk;
+        first_cta = t0 / p.units_per_cta;
+        last_cta = (t0 + sched.nsk - 1) / p.units_per_cta;
+      }
       if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4)) break;
       tcgen05_fence_after();
       const uint32_t t_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -653,10 +661,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
 #pragma unroll
           for (int m = 0; m < BN; ++m)
             if (m < p.M) __stcg(mine + (size_t)m * kLanes + lrow, v[m]);
-          // CTAs whose unit range intersects this tile
-          const int t0 = s.lane_tile * sched.nsk;
-          const int first_cta = t0 / p.units_per_cta;
-          const int last_cta = (t0 + sched.nsk - 1) / p.units_per_cta;
           if (p.comm.world > 1) {
             // the exchange below is a whole-CTA protocol: one arrival counter per tile
             __threadfence();
