@@ -160,7 +160,8 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
  * finished; it reads A, bias and residual only after that kernel completed, and W too unless
  * flags has EB_GEMM_STATIC_W.
  * For M <= 128 (generation steps) the kernel streams W exactly once, split evenly over all SMs
- * (stream-K over 128-row tiles), and combines the partial sums of tiles shared by several CTAs
+ * (stream-K over 128-row tiles; a K of at most 1280 is not cut, one CTA per tile), and combines
+ * the partial sums of tiles shared by several CTAs
  * through `workspace`: at least eb_gemm_workspace_bytes(M,N,K) bytes, 16-byte aligned,
  * zero-filled once before first use (the kernel leaves it reusable; summation order is fixed,
  * results are deterministic).  Calls that share a workspace must not overlap on the device.
