@@ -42,3 +42,37 @@ def test_cpu_tensors_are_rejected():
     from energonai_b200.kernel import scale_mask_softmax
     with pytest.raises(RuntimeError):
         scale_mask_softmax(1, 4, 1, torch.zeros(1, 1, 4, 4), torch.tensor([4], dtype=torch.int32))
+
+
+def test_chain_op_struct_matches_the_header(tmp_path):
+    """The ctypes mirror of struct eb_chain_op has the size and field offsets a C compiler gives
+    the declaration in the header (the header itself compiles as plain C)."""
+    import shutil
+    import subprocess
+    from energonai_b200.chain import ChainOp
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    fields = [name for name, _ in ChainOp._fields_]
+    src = tmp_path / "layout.c"
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{_lib.HEADER}"', 'int main(void) {',
+             '  printf("%zu\\n", sizeof(eb_chain_op));']
+    lines += [f'  printf("%zu\\n", offsetof(eb_chain_op, {f}));' for f in fields]
+    lines += ['  return 0;', '}']
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", str(src), "-o", str(exe)], check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert int(out[0]) == ctypes.sizeof(ChainOp)
+    for f, off in zip(fields, out[1:]):
+        assert int(off) == getattr(ChainOp, f).offset, f
+
+
+def test_new_entry_points_validate_before_any_cuda_call():
+    L = _lib.lib()
+    # eb_gemm_ln: the folded vectors are required, and only generation-step batches are served
+    assert L.eb_gemm_ln(None, 8, None, 8, None, 8, None, None, 1e-5, None, 0, 4, 8, 8, _lib.F16, _lib.F16, 0, 0, 0, None, 0,
+                        None, 0, None) == -1
+    assert "ln_colsum" in _lib.last_error()
+    assert L.eb_decode_chain(None, 0, 16, _lib.F16, None, 0, None) == -1
+    assert L.eb_decode_chain_workspace_bytes(None, 0, 16) == 0
