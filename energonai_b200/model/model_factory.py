@@ -302,12 +302,21 @@ def create_pipeline_model(depth: int = 48, layer_partitions=None, **model_kwargs
     if layer_partitions is not None:
         raise RuntimeError("pipeline partitioning is not supported; run with one pipeline stage")
     model_kwargs = dict(model_kwargs)
-    for k in ("checkpoint",):
-        if model_kwargs.get(k):
-            raise RuntimeError("checkpoint loading is not implemented; load a state_dict with the reference's names")
     model_kwargs.update(first=True, last=True, depth=depth)
     model = PipelineModel(**model_kwargs)
-    return model.cuda() if torch.cuda.is_available() else model
+    model = model.cuda() if torch.cuda.is_available() else model
+    # model_factory.py:212-224: a checkpoint is loaded only when the model family is named
+    if model_kwargs.get("checkpoint") and model_kwargs.get("model_name"):
+        from ..utils import load_175b, load_checkpoint, processing_HF_GPT, processing_OPT
+        if not os.path.exists(model_kwargs["checkpoint"]):
+            raise FileNotFoundError(f"checkpoint {model_kwargs['checkpoint']} not found")
+        if model_kwargs["model_name"] == "opt-175b":
+            load_175b(model_kwargs["checkpoint"], model)
+        else:
+            preprocess_fn = {"hf_gpt2": processing_HF_GPT, "opt": processing_OPT}.get(model_kwargs["model_name"])
+            extra = {k: v for k, v in model_kwargs.items() if k == "prefix"}
+            load_checkpoint(model_kwargs["checkpoint"], model, preprocess_fn=preprocess_fn, **extra)
+    return model
 
 
 def _opt(hidden, depth, heads, **kwargs):
