@@ -44,29 +44,40 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
     const int packs_vis = (nvis + VEC - 1) / VEC;
 
     if (VPL > 0) {
-      P cache[VPL > 0 ? VPL : 1];
+      // The kernel is bound by instruction issue, not by memory, unless the per-element work is
+      // kept minimal: a pack is converted and scaled once, the keys of the one pack that
+      // straddles the end of the visible prefix are set to -inf there (so the later phases need
+      // no comparisons: exp(-inf - max) is an exact 0), every exponential is evaluated once and
+      // kept in its register, and packs that lie wholly behind the prefix are stored as zeros
+      // without any arithmetic.
+      float x[VPL > 0 ? VPL : 1][VEC];
       float mx = -FLT_MAX;
 #pragma unroll
       for (int t = 0; t < VPL; ++t) {
         const int v = lane + 32 * t;
         if (v < packs_vis) {
-          cache[t] = rp[v];
+          const P c = rp[v];
 #pragma unroll
-          for (int e = 0; e < VEC; ++e)
-            if (v * VEC + e < nvis) mx = fmaxf(mx, to_f32<T>(cache[t].e[e]) * scale);
+          for (int e = 0; e < VEC; ++e) x[t][e] = to_f32<T>(c.e[e]) * scale;
+          if ((v + 1) * VEC > nvis) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              if (v * VEC + e >= nvis) x[t][e] = -INFINITY;
+          }
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) mx = fmaxf(mx, x[t][e]);
         }
       }
       mx = warp_max(mx);
-      // exp is evaluated twice (once for the sum, once for the output) instead of keeping the
-      // fp32 exponentials: fewer registers, more rows in flight per SM
       float sum = 0.f;
 #pragma unroll
       for (int t = 0; t < VPL; ++t) {
-        const int v = lane + 32 * t;
-        if (v < packs_vis) {
+        if (lane + 32 * t < packs_vis) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e)
-            if (v * VEC + e < nvis) sum += __expf(to_f32<T>(cache[t].e[e]) * scale - mx);
+          for (int e = 0; e < VEC; ++e) {
+            x[t][e] = __expf(x[t][e] - mx);
+            sum += x[t][e];
+          }
         }
       }
       sum = warp_sum(sum);
@@ -76,11 +87,12 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
         const int v = lane + 32 * t;
         if (v < packs_row) {
           P out;
+          if (v < packs_vis) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            float p = 0.f;
-            if (v < packs_vis && v * VEC + e < nvis) p = __expf(to_f32<T>(cache[t].e[e]) * scale - mx) * inv;
-            out.e[e] = from_f32<T>(p);
+            for (int e = 0; e < VEC; ++e) out.e[e] = from_f32<T>(x[t][e] * inv);
+          } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) out.e[e] = from_f32<T>(0.f);
           }
           rp[v] = out;
         }
