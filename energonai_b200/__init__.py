@@ -6,7 +6,7 @@ declared in include/energon_b200.h; there is no CPU or PyTorch fallback.
 """
 __version__ = "0.1.0"
 
-from .batch_mgr import BatchManager, SubmitEntry
+from .batch_mgr import BatchManager, BatchManagerForGeneration, SubmitEntry
 from .task import TaskEntry
 
 
@@ -18,4 +18,4 @@ def __getattr__(name):
     raise AttributeError(name)
 
 
-__all__ = ["BatchManager", "launch_engine", "SubmitEntry", "TaskEntry", "QueueFullError"]
+__all__ = ["BatchManager", "BatchManagerForGeneration", "launch_engine", "SubmitEntry", "TaskEntry", "QueueFullError"]

@@ -1,10 +1,13 @@
 """One engine life cycle in a fresh process (torch RPC cannot be re-initialised reliably inside
 one process, which is also why the reference runs its engine tests one file per process):
 
-    python -m energonai_b200.testing.engine_check <tp_world_size>
+    python -m energonai_b200.testing.engine_check <tp_world_size> [generation]
 
 Launches workers, submits requests through a batching manager, checks BoringModel's closed form
-(4x + 1), checks QueueFullError, shuts down.  Exit code 0 on success."""
+(4x + 1), checks QueueFullError, shuts down.  With `generation`, the engine runs
+BatchManagerForGeneration (length buckets, scan window) in front of a model whose answer to a
+request does not depend on its batch: every request gets its own prompt and its own number of
+new tokens back, however the requests were grouped.  Exit code 0 on success."""
 import asyncio
 import socket
 import sys
@@ -63,5 +66,36 @@ def main(tp_world_size):
     print("engine ok", tp_world_size, flush=True)
 
 
+def main_generation(tp_world_size):
+    import random
+    from energonai_b200 import BatchManagerForGeneration
+    from energonai_b200.testing.models import EchoGenerator, expected_new_tokens
+    rng = random.Random(3)
+    reqs = {}
+    for uid in range(12):
+        n = rng.randint(1, 40)
+        reqs[uid] = dict(input_ids=[rng.randint(2, 999) for _ in range(n)], attention_mask=[1] * n, top_k=1, top_p=None,
+                         temperature=None, max_tokens=rng.randint(1, 9))
+    mgr = BatchManagerForGeneration(max_batch_size=4, pad_token_id=0, bucket_size=16, scan_window=4)
+    engine = launch_engine(tp_world_size, 1, "127.0.0.1", free_port(), free_port(), EchoGenerator, batch_manager=mgr)
+    try:
+        for uid, r in reqs.items():
+            engine.submit(uid, r)
+        for uid, r in reqs.items():
+            out = engine.get(uid)
+            n, new = len(r["input_ids"]), r["max_tokens"]
+            width = out.numel() - new
+            assert width % 16 == 0 and width >= n, (uid, out.shape)
+            assert not out[:width - n].any() and out[width - n:width].tolist() == r["input_ids"], uid
+            want = expected_new_tokens(torch.tensor(sum(r["input_ids"])), torch.arange(new))
+            assert torch.equal(out[width:], want), (uid, out[width:], want)
+    finally:
+        engine.shutdown()
+    print("engine generation ok", tp_world_size, flush=True)
+
+
 if __name__ == "__main__":
-    main(int(sys.argv[1]))
+    if len(sys.argv) > 2 and sys.argv[2] == "generation":
+        main_generation(int(sys.argv[1]))
+    else:
+        main(int(sys.argv[1]))

@@ -26,3 +26,20 @@ def get_correct_output(x: torch.Tensor, pp_world_size: int = 1) -> torch.Tensor:
     for _ in range(pp_world_size):
         x = x * 4 + 1
     return x
+
+
+class EchoGenerator(nn.Module):
+    """Stand-in for a generation model behind the engine: takes the keyword arguments a
+    PipelineModel takes and returns [batch, max_tokens] token ids, each row its (padded) prompt
+    followed by tokens that depend only on that row's own unpadded prompt, so the answer to a
+    request does not depend on which other requests it was batched with."""
+
+    def forward(self, input_ids=None, attention_mask=None, max_tokens=0, top_k=None, top_p=None, temperature=None):
+        width = input_ids.shape[1]
+        seed = (input_ids * attention_mask).sum(1, keepdim=True)
+        steps = torch.arange(max_tokens - width, device=input_ids.device)[None, :]
+        return torch.cat([input_ids, expected_new_tokens(seed, steps)], 1)
+
+
+def expected_new_tokens(seed, steps):
+    return 2 + (seed * 7 + steps * 13) % 997

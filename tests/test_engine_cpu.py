@@ -19,6 +19,13 @@ def test_engine_life_cycle(tp_world_size):
     assert r.returncode == 0 and f"engine ok {tp_world_size}" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
 
 
+def test_engine_with_the_generation_batch_manager():
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "energonai_b200.testing.engine_check", "1", "generation"], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0 and "engine generation ok 1" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
 def test_pipeline_parallelism_is_rejected():
     from energonai_b200.engine import AsyncEngine
     with pytest.raises(RuntimeError, match="pp_world_size"):
