@@ -122,6 +122,11 @@ def membound():
     vis = int(sum(int(l) * (int(l) + 1) // 2 for l in lens.tolist()))
     report("scale_mask_softmax [32,16,512,512] fp16 (visible reads + row writes)", (vis + V * S) * H * 2,
            timed(lambda: EK.scale_mask_softmax(B, S, H, scores, lens)))
+    # the BERT-style use of configuration 2: key-length mask only, every query row written
+    from ._lib import SM_ALLROWS, SM_KEYLEN
+    report("scale_mask_softmax [32,16,512,512] fp16, key-length mask, all rows (visible reads + row writes)",
+           (V + B * S) * S * H * 2,
+           timed(lambda: EK.scale_mask_softmax(B, S, H, scores, lens, flags=SM_KEYLEN | SM_ALLROWS, scale=0.125)))
     for rows, n in ((B * S, 1024), (8192, 5120)):
         xx = torch.randn(rows, n, device="cuda", dtype=torch.float16)
         g, b = torch.ones(n, device="cuda", dtype=torch.float16), torch.zeros(n, device="cuda", dtype=torch.float16)
