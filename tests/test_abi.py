@@ -76,3 +76,11 @@ def test_new_entry_points_validate_before_any_cuda_call():
     assert "ln_colsum" in _lib.last_error()
     assert L.eb_decode_chain(None, 0, 16, _lib.F16, None, 0, None) == -1
     assert L.eb_decode_chain_workspace_bytes(None, 0, 16) == 0
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    """No CPU or PyTorch fallback: without the built library every kernel call raises."""
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libenergon_b200.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.lib()
