@@ -12,10 +12,11 @@ from .task import TaskEntry
 
 def __getattr__(name):
     # launch_engine and QueueFullError pull in torch.distributed.rpc; import them on first use
-    if name in ("launch_engine", "QueueFullError", "AsyncEngine"):
+    if name in ("launch_engine", "QueueFullError", "AsyncEngine", "WorkerFailedError"):
         from . import engine
         return getattr(engine, name)
     raise AttributeError(name)
 
 
-__all__ = ["BatchManager", "BatchManagerForGeneration", "launch_engine", "SubmitEntry", "TaskEntry", "QueueFullError"]
+__all__ = ["BatchManager", "BatchManagerForGeneration", "launch_engine", "SubmitEntry", "TaskEntry", "QueueFullError",
+           "WorkerFailedError"]

@@ -5,7 +5,12 @@ torch RPC and hands results back by request id.
 Kept: constructor and method names, `submit` / `wait` / `get` / `shutdown`, QueueFullError, the
 BatchManager hooks, "same batch to every rank, rank 0's answer is returned" (engine.py:79-80,
 94-97).  Changed: one pipeline stage only (pp_world_size must be 1), blocking queues instead of
-10 ms polling, workers stop through an RPC that sets an event instead of raising SIGINT."""
+10 ms polling, workers stop through an RPC that sets an event instead of raising SIGINT.
+Added (the reference waits forever in both cases): a batch whose model call raised is answered
+with that error (`RemoteFailure` -> RuntimeError from `get` / `wait`, the worker keeps serving),
+and a worker process that exits while the engine runs makes every pending and later `get` /
+`wait` raise WorkerFailedError; `shutdown` then tears the RPC layer down without waiting for
+the dead peer."""
 import asyncio
 import threading
 import time
@@ -17,7 +22,7 @@ import torch.nn as nn
 
 from .batch_mgr import BatchManager, SubmitEntry
 from .pipe import Pipe
-from .task import TaskEntry
+from .task import RemoteFailure, TaskEntry
 from .worker import _request_stop, launch_workers, rpc_options
 
 
@@ -25,10 +30,14 @@ class QueueFullError(Exception):
     pass
 
 
+class WorkerFailedError(RuntimeError):
+    """A worker process exited (or became unreachable) while the engine was running."""
+
+
 class AsyncEngine:
     def __init__(self, tp_world_size: int, pp_world_size: int, master_host: str, rpc_port: int, n_proc_per_node: int,
                  batch_manager: Optional[BatchManager] = None, pipe_size: int = 1, queue_size: int = 0,
-                 rpc_disable_shm: bool = True) -> None:
+                 rpc_disable_shm: bool = True, worker_procs=()) -> None:
         if pp_world_size != 1:
             raise RuntimeError("pipeline parallelism is outside this package: pp_world_size must be 1")
         self.batch_manager = batch_manager if batch_manager is not None else BatchManager()
@@ -48,6 +57,8 @@ class AsyncEngine:
         self.batch_info: Dict[Hashable, Any] = {}
         self.completion_map: Dict[Hashable, Any] = {}
         self.running = True
+        self.worker_procs = list(worker_procs)          # local worker processes, watched for exits
+        self.failed: Optional[str] = None
         self.submit_thread = threading.Thread(target=self._submit_loop, daemon=True)
         self.completion_thread = threading.Thread(target=self._completion_loop, daemon=True)
         self.submit_thread.start()
@@ -62,28 +73,51 @@ class AsyncEngine:
                     return
                 task_entry, info = self.batch_manager.make_batch(self.submit_queue)
                 self.batch_info[task_entry.uids] = (info, len(task_entry.uids), time.time())
-            for pipe in self.submit_pipes:               # the same batch goes to every tensor-parallel rank
-                pipe.send(task_entry)
+            try:
+                for pipe in self.submit_pipes:           # the same batch goes to every tensor-parallel rank
+                    pipe.send(task_entry)
+            except Exception as exc:                     # the peer is gone: RPC raises instead of delivering
+                self._fail(f"sending a batch to a worker failed: {type(exc).__name__}: {exc}")
+                return
+
+    def _fail(self, why: str) -> None:
+        with self.lock:
+            if self.failed is None:
+                self.failed = why
+
+    def _check_workers(self) -> None:
+        for rank, proc in enumerate(self.worker_procs):
+            if proc.exitcode is not None and self.running:
+                self._fail(f"worker process {rank} exited with code {proc.exitcode}")
+
+    def _recv(self, pipe: Pipe):
+        """Next item of a completion pipe, or None once the engine stops or has failed."""
+        while self.running and self.failed is None:
+            try:
+                return pipe.recv(timeout=0.1)
+            except RuntimeError:
+                self._check_workers()
+        return None
 
     def _completion_loop(self) -> None:
-        while self.running:
-            try:
-                first: TaskEntry = self.completion_pipes[0].recv(timeout=0.1)
-            except RuntimeError:
-                continue
-            for pipe in self.completion_pipes[1:]:       # drain the other ranks' copies of the same batch
-                while self.running:
-                    try:
-                        pipe.recv(timeout=0.1)
-                        break
-                    except RuntimeError:
-                        continue
+        while self.running and self.failed is None:
+            copies = [self._recv(pipe) for pipe in self.completion_pipes]    # every rank's copy of one batch
+            if any(c is None for c in copies):
+                return
+            first: TaskEntry = copies[0]
+            failure = next((c.batch for c in copies if isinstance(c.batch, RemoteFailure)), None)
             with self.lock:
                 info, _, _ = self.batch_info.pop(first.uids)
-                for uid, output in self.batch_manager.split_batch(first, **info):
-                    self.completion_map[uid] = output
+                if failure is not None:
+                    for uid in first.uids:
+                        self.completion_map[uid] = failure
+                else:
+                    for uid, output in self.batch_manager.split_batch(first, **info):
+                        self.completion_map[uid] = output
 
     def submit(self, uid: Hashable, data: Any) -> None:
+        if self.failed is not None:
+            raise WorkerFailedError(self.failed)
         assert self.submit_thread.is_alive()
         with self.work:
             assert uid not in self.completion_map
@@ -95,7 +129,12 @@ class AsyncEngine:
     def _take(self, uid: Hashable):
         with self.lock:
             if uid in self.completion_map:
-                return True, self.completion_map.pop(uid)
+                out = self.completion_map.pop(uid)
+                if isinstance(out, RemoteFailure):
+                    raise RuntimeError(f"request {uid!r} failed on worker {out.rank}: {out.message}")
+                return True, out
+            if self.failed is not None:
+                raise WorkerFailedError(self.failed)
         return False, None
 
     async def wait(self, uid: Hashable) -> Any:
@@ -118,25 +157,50 @@ class AsyncEngine:
                 return
             self.running = False
             self.work.notify_all()
-        for i in range(self.world_size):
-            trpc.rpc_sync(f"worker{i}", _request_stop)
-        trpc.shutdown()
+        if self.failed is None:
+            self._check_workers()
+        if self.failed is None:
+            for i in range(self.world_size):
+                trpc.rpc_sync(f"worker{i}", _request_stop)
+            trpc.shutdown()
+        else:
+            # a peer is gone: ask the others to stop without waiting for answers, and do not
+            # wait for the dead one in the RPC layer's own farewell round
+            for i in range(self.world_size):
+                try:
+                    trpc.rpc_async(f"worker{i}", _request_stop, timeout=2.0)
+                except Exception:
+                    pass
+            trpc.shutdown(graceful=False)
         self.submit_thread.join()
         self.completion_thread.join()
+        for proc in self.worker_procs:
+            proc.join(timeout=10)
 
 
-def launch_engine(tp_world_size: int, pp_world_size: int, master_host: str, master_port: int, rpc_port: int,
-                  model_fn: Callable[..., nn.Module], n_nodes: int = 1, node_rank: int = 0,
-                  batch_manager: Optional[BatchManager] = None, pipe_size: int = 1, queue_size: int = 0,
-                  rpc_disable_shm: bool = True, **model_kwargs: Any) -> Optional[AsyncEngine]:
+def launch_engine(tp_world_size: Optional[int] = None, pp_world_size: int = 1, master_host: str = "127.0.0.1",
+                  master_port: int = 29500, rpc_port: int = 29501, model_fn: Callable[..., nn.Module] = None,
+                  n_nodes: int = 1, node_rank: int = 0, batch_manager: Optional[BatchManager] = None, pipe_size: int = 1,
+                  queue_size: int = 0, rpc_disable_shm: bool = True, tp_init_size: Optional[int] = None,
+                  pp_init_size: Optional[int] = None, **model_kwargs: Any) -> Optional[AsyncEngine]:
+    """energonai/engine.py:157-168, same positional order.  `tp_init_size` / `pp_init_size` (the
+    names of the reference's older server configurations) are accepted for the two sizes."""
+    if tp_world_size is None:
+        tp_world_size = 1 if tp_init_size is None else tp_init_size
+    elif tp_init_size is not None and tp_init_size != tp_world_size:
+        raise ValueError(f"tp_world_size={tp_world_size} and tp_init_size={tp_init_size} disagree")
+    if pp_init_size is not None:
+        pp_world_size = pp_init_size
+    if model_fn is None:
+        raise TypeError("launch_engine needs model_fn")
     world_size = tp_world_size * pp_world_size
     assert world_size % n_nodes == 0
     n_proc_per_node = world_size // n_nodes
-    launch_workers(tp_world_size, pp_world_size, master_host, master_port, rpc_port, model_fn,
-                   n_proc_per_node=n_proc_per_node, node_rank=node_rank, pipe_size=pipe_size,
-                   rpc_disable_shm=rpc_disable_shm, **model_kwargs)
+    procs = launch_workers(tp_world_size, pp_world_size, master_host, master_port, rpc_port, model_fn,
+                           n_proc_per_node=n_proc_per_node, node_rank=node_rank, pipe_size=pipe_size,
+                           rpc_disable_shm=rpc_disable_shm, **model_kwargs)
     if node_rank == 0:
         return AsyncEngine(tp_world_size, pp_world_size, master_host, rpc_port, n_proc_per_node,
                            batch_manager=batch_manager, pipe_size=pipe_size, queue_size=queue_size,
-                           rpc_disable_shm=rpc_disable_shm)
+                           rpc_disable_shm=rpc_disable_shm, worker_procs=procs)
     return None

@@ -1,13 +1,16 @@
 """One engine life cycle in a fresh process (torch RPC cannot be re-initialised reliably inside
 one process, which is also why the reference runs its engine tests one file per process):
 
-    python -m energonai_b200.testing.engine_check <tp_world_size> [generation]
+    python -m energonai_b200.testing.engine_check <tp_world_size> [generation|failure]
 
 Launches workers, submits requests through a batching manager, checks BoringModel's closed form
 (4x + 1), checks QueueFullError, shuts down.  With `generation`, the engine runs
 BatchManagerForGeneration (length buckets, scan window) in front of a model whose answer to a
 request does not depend on its batch: every request gets its own prompt and its own number of
-new tokens back, however the requests were grouped.  Exit code 0 on success."""
+new tokens back, however the requests were grouped.  With `failure`, a request the model rejects
+is answered with a RuntimeError while the worker keeps serving, and a worker process that dies
+turns pending and later requests into WorkerFailedError instead of a hang; shutdown still
+returns.  Exit code 0 on success."""
 import asyncio
 import socket
 import sys
@@ -94,8 +97,45 @@ def main_generation(tp_world_size):
     print("engine generation ok", tp_world_size, flush=True)
 
 
+def main_failure():
+    import time
+    from energonai_b200 import WorkerFailedError
+    from energonai_b200.testing.models import FlakyModel
+    engine = launch_engine(tp_init_size=1, master_host="127.0.0.1", master_port=free_port(), rpc_port=free_port(),
+                           model_fn=FlakyModel)
+    try:
+        engine.submit("ok", torch.ones(4))
+        assert torch.equal(engine.get("ok"), get_correct_output(torch.ones(4)))
+        engine.submit("rejected", torch.full((4,), -1.0))
+        try:
+            engine.get("rejected")
+            raise AssertionError("a rejected request must raise")
+        except RuntimeError as exc:
+            assert "request rejected by the model" in str(exc) and "'rejected'" in str(exc), exc
+        engine.submit("after", torch.zeros(4))                       # the worker is still serving
+        assert torch.equal(engine.get("after"), get_correct_output(torch.zeros(4)))
+        engine.submit("crash", torch.full((4,), -2.0))
+        t0 = time.time()
+        try:
+            engine.get("crash")
+            raise AssertionError("a dead worker must raise")
+        except WorkerFailedError as exc:
+            assert "exited with code 7" in str(exc) or "failed" in str(exc), exc
+        assert time.time() - t0 < 30
+        try:
+            engine.submit("later", torch.ones(4))
+            raise AssertionError("submitting to a failed engine must raise")
+        except WorkerFailedError:
+            pass
+    finally:
+        engine.shutdown()
+    print("engine failure ok", flush=True)
+
+
 if __name__ == "__main__":
-    if len(sys.argv) > 2 and sys.argv[2] == "generation":
+    if len(sys.argv) > 2 and sys.argv[2] == "failure":
+        main_failure()
+    elif len(sys.argv) > 2 and sys.argv[2] == "generation":
         main_generation(int(sys.argv[1]))
     else:
         main(int(sys.argv[1]))

@@ -43,3 +43,18 @@ class EchoGenerator(nn.Module):
 
 def expected_new_tokens(seed, steps):
     return 2 + (seed * 7 + steps * 13) % 997
+
+
+class FlakyModel(nn.Module):
+    """4x + 1 like BoringModel at tensor-parallel size 1, except for two marker inputs: a first
+    element of -1 raises (a request the model rejects), a first element of -2 ends the worker
+    process at once (a crashed worker).  Used to test what the engine tells its callers."""
+
+    def forward(self, x):
+        marker = float(x.reshape(-1)[0])
+        if marker == -1.0:
+            raise ValueError("request rejected by the model")
+        if marker == -2.0:
+            import os
+            os._exit(7)
+        return x * 4 + 1

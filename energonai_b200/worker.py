@@ -15,7 +15,7 @@ import torch.multiprocessing as mp
 
 from . import tp
 from .pipe import Pipe
-from .task import TaskEntry
+from .task import RemoteFailure, TaskEntry
 
 _stop = threading.Event()
 
@@ -75,9 +75,12 @@ class Worker:
                     task: TaskEntry = self.input_pipe.recv(timeout=0.05)
                 except RuntimeError:
                     continue
-                with torch.inference_mode():
-                    out = self._forward(task.batch)
-                out = out.cpu() if torch.is_tensor(out) else out
+                try:
+                    with torch.inference_mode():
+                        out = self._forward(task.batch)
+                    out = out.cpu() if torch.is_tensor(out) else out
+                except Exception as exc:                 # answer the batch with the error, keep serving
+                    out = RemoteFailure(self.global_rank, f"{type(exc).__name__}: {exc}")
                 self.output_pipe.send(TaskEntry(task.uids, out))
         finally:
             trpc.shutdown()

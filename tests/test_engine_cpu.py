@@ -26,6 +26,22 @@ def test_engine_with_the_generation_batch_manager():
     assert r.returncode == 0 and "engine generation ok 1" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
 
 
+def test_engine_reports_rejected_requests_and_dead_workers():
+    """Failures are made on the host: a model call that raises, and a worker process that exits."""
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "energonai_b200.testing.engine_check", "1", "failure"], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0 and "engine failure ok" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_launch_engine_size_aliases_are_checked_before_anything_starts():
+    from energonai_b200.engine import launch_engine
+    with pytest.raises(ValueError, match="disagree"):
+        launch_engine(2, 1, "127.0.0.1", 1, 1, lambda: None, tp_init_size=4)
+    with pytest.raises(TypeError, match="model_fn"):
+        launch_engine(tp_init_size=1)
+
+
 def test_pipeline_parallelism_is_rejected():
     from energonai_b200.engine import AsyncEngine
     with pytest.raises(RuntimeError, match="pp_world_size"):
