@@ -136,5 +136,37 @@ def membound():
                timed(lambda: layer_norm_forward(xx, g, b, 1e-5, residual=rr, add_bias=b, return_sum=True)))
 
 
+def softmax():
+    """scale_mask_softmax at configuration 2's shape timed alone: eight distinct 268 MB score
+    tensors (2.1 GB, far beyond L2) processed back to back between one pair of CUDA events, so
+    neither host launch latency nor cache residency is in the figure."""
+    import numpy as np
+    from . import kernel as EK
+    from ._lib import SM_ALLROWS, SM_KEYLEN
+    B, H, S = 32, 16, 512
+    rng = np.random.default_rng(1)
+    lens_h = rng.integers(32, S + 1, B).astype(np.int32)
+    lens = torch.from_numpy(lens_h).cuda()
+    V = int(lens_h.sum())
+    vis = int(sum(int(n) * (int(n) + 1) // 2 for n in lens_h))
+    bufs = [torch.randn(B, H, S, S, device="cuda", dtype=torch.float16) for _ in range(8)]
+    cases = (("causal + length mask (the reference's mode)", {}, (vis + V * S) * H * 2),
+             ("key-length mask, all rows", dict(flags=SM_KEYLEN | SM_ALLROWS, scale=0.125), (V + B * S) * S * H * 2))
+    for name, kw, nbytes in cases:
+        for b in bufs[:2]:
+            EK.scale_mask_softmax(B, S, H, b, lens, **kw)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for b in bufs:
+            EK.scale_mask_softmax(B, S, H, b, lens, **kw)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / len(bufs)
+        print(f"scale_mask_softmax [32,16,512,512] fp16, {name}: {us:.1f} us per launch, {nbytes / 1e6:.1f} MB algorithmic, "
+              f"{nbytes / us / 1e3:.0f} GB/s")
+
+
 if __name__ == "__main__":
-    {"gemm_decode": gemm_decode, "gemm_prefill": gemm_prefill, "attention": attention, "membound": membound}[sys.argv[1]]()
+    {"gemm_decode": gemm_decode, "gemm_prefill": gemm_prefill, "attention": attention, "membound": membound,
+     "softmax": softmax}[sys.argv[1]]()
