@@ -15,6 +15,8 @@
 //
 // Q, K and V are addressed as [batch][row][head*D + d] with independent batch and row strides,
 // so they may be column slices of one fused projection / cache buffer.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace eb {
@@ -601,8 +603,12 @@ extern "C" int eb_attention_decode_noalloc(const void *q, const void *k, const v
                                            int heads, int kv_len, const int32_t *kv_len_device, int head_dim,
                                            float scale, int dtype, int nsplit, void *stream) {
   // In host code the array's name is only a handle for the runtime, not a device address; the
-  // address is looked up once per device, with that device current, and remembered.
+  // address is looked up once per device, with that device current, and remembered.  The
+  // look-up and the one-time clearing of the counters run under a lock, so two host threads
+  // making their first call on a device cannot both enqueue the clearing (the later one could
+  // otherwise zero counters under the other thread's kernel).
   static void *device_ptr[64] = {};
+  static std::mutex setup_lock;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     cudaGetLastError();
@@ -614,22 +620,29 @@ extern "C" int eb_attention_decode_noalloc(const void *q, const void *k, const v
                 "attention_decode_noalloc: batch %d x heads %d x nsplit %d needs %zu bytes of scratch, the built-in "
                 "array holds %zu; lower nsplit or use eb_attention_decode with a caller-provided scratch",
                 batch, heads, nsplit, need, (size_t)kStaticScratchBytes);
-  if (device_ptr[dev] == nullptr) {
-    void *ptr = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_decode_scratch);
-    if (e != cudaSuccess || ptr == nullptr) {
-      cudaGetLastError();
-      return fail(EB_ECUDA, "attention_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+  if (need == 0)   // a single split uses no scratch: nothing to look up or clear
+    return eb_attention_decode(q, k, v, out, mask, q_batch_stride, q_row_stride, k_batch_stride, k_row_stride,
+                               v_batch_stride, v_row_stride, o_batch_stride, mask_batch_stride, batch, heads, kv_len,
+                               kv_len_device, head_dim, scale, dtype, nsplit, nullptr, 0, stream);
+  {
+    std::lock_guard<std::mutex> guard(setup_lock);
+    if (device_ptr[dev] == nullptr) {
+      void *ptr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_decode_scratch);
+      if (e != cudaSuccess || ptr == nullptr) {
+        cudaGetLastError();
+        return fail(EB_ECUDA, "attention_decode_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      }
+      // The arrival counters at the head of the array must start at zero.  A freshly loaded image
+      // is zero already; clearing them here also covers a process that reuses the device after an
+      // aborted call.  (Stream-ordered, so this first call should not be inside a stream capture.)
+      e = cudaMemsetAsync(ptr, 0, 64 * 1024, as_stream(stream));
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(EB_ECUDA, "attention_decode_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
+      }
+      device_ptr[dev] = ptr;
     }
-    // The arrival counters at the head of the array must start at zero.  A freshly loaded image
-    // is zero already; clearing them here also covers a process that reuses the device after an
-    // aborted call.  (Stream-ordered, so this first call should not be inside a stream capture.)
-    e = cudaMemsetAsync(ptr, 0, 64 * 1024, as_stream(stream));
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      return fail(EB_ECUDA, "attention_decode_noalloc: clearing the counters failed: %s", cudaGetErrorString(e));
-    }
-    device_ptr[dev] = ptr;
   }
   return eb_attention_decode(q, k, v, out, mask, q_batch_stride, q_row_stride, k_batch_stride, k_row_stride,
                              v_batch_stride, v_row_stride, o_batch_stride, mask_batch_stride, batch, heads, kv_len,

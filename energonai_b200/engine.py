@@ -43,11 +43,15 @@ class AsyncEngine:
         self.batch_manager = batch_manager if batch_manager is not None else BatchManager()
         assert isinstance(self.batch_manager, BatchManager)
         self.world_size = tp_world_size * pp_world_size
-        trpc.init_rpc("master", rank=0, world_size=self.world_size + 1,
-                      rpc_backend_options=rpc_options(master_host, rpc_port, rpc_disable_shm))
+        self.worker_procs = list(worker_procs)          # local worker processes, watched for exits
+        self._start_rpc(master_host, rpc_port, rpc_disable_shm)
         self.completion_pipes: List[Pipe] = [Pipe(f"{i}_to_m", f"worker{i}", "master") for i in range(self.world_size)]
-        for pipe in self.completion_pipes:
-            assert pipe.recv() == 0                      # every worker reports pipeline rank 0
+        for rank, pipe in enumerate(self.completion_pipes):
+            hello = self._recv_hello(rank, pipe)
+            if isinstance(hello, RemoteFailure):         # the worker could not build its model shard
+                self._abandon_rpc()
+                raise WorkerFailedError(f"worker {hello.rank} failed to start: {hello.message}")
+            assert hello == 0                            # every worker reports pipeline rank 0
         self.submit_pipes: List[Pipe] = [Pipe(f"m_to_{i}", "master", f"worker{i}", max_size=pipe_size)
                                          for i in range(self.world_size)]
         self.queue_size = queue_size
@@ -57,12 +61,63 @@ class AsyncEngine:
         self.batch_info: Dict[Hashable, Any] = {}
         self.completion_map: Dict[Hashable, Any] = {}
         self.running = True
-        self.worker_procs = list(worker_procs)          # local worker processes, watched for exits
         self.failed: Optional[str] = None
         self.submit_thread = threading.Thread(target=self._submit_loop, daemon=True)
         self.completion_thread = threading.Thread(target=self._completion_loop, daemon=True)
         self.submit_thread.start()
         self.completion_thread.start()
+
+    # -- start-up: a worker that dies before it joins (model_fn raised before the RPC layer was
+    # up, the process group could not form, the process was killed) must not hang the caller --
+    def _dead_worker(self) -> Optional[str]:
+        for rank, proc in enumerate(self.worker_procs):
+            if proc.exitcode is not None:
+                return f"worker process {rank} exited with code {proc.exitcode} during start-up"
+        return None
+
+    def _start_rpc(self, master_host: str, rpc_port: int, rpc_disable_shm: bool) -> None:
+        """init_rpc waits for every peer; it runs in a helper thread while this one watches the
+        worker processes, so a worker that never arrives ends the wait with an error."""
+        result: Dict[str, Any] = {}
+
+        def join() -> None:
+            try:
+                trpc.init_rpc("master", rank=0, world_size=self.world_size + 1,
+                              rpc_backend_options=rpc_options(master_host, rpc_port, rpc_disable_shm))
+                result["ok"] = True
+            except Exception as exc:                     # noqa: BLE001 (reported to the caller below)
+                result["error"] = exc
+
+        t = threading.Thread(target=join, daemon=True)
+        t.start()
+        while t.is_alive():
+            t.join(0.1)
+            why = self._dead_worker()
+            if why is not None and t.is_alive():
+                raise WorkerFailedError(why)             # the helper thread stays behind, blocked
+        if "error" in result:
+            raise WorkerFailedError(f"joining the RPC group failed: {result['error']}")
+
+    def _recv_hello(self, rank: int, pipe: Pipe):
+        while True:
+            try:
+                return pipe.recv(timeout=0.1)
+            except RuntimeError:
+                why = self._dead_worker()
+                if why is not None:
+                    self._abandon_rpc()
+                    raise WorkerFailedError(why) from None
+
+    def _abandon_rpc(self) -> None:
+        for i in range(self.world_size):
+            try:
+                trpc.rpc_async(f"worker{i}", _request_stop, timeout=2.0)
+            except Exception:                            # noqa: BLE001
+                pass
+        try:
+            trpc.shutdown(graceful=False)
+        except Exception:                                # noqa: BLE001
+            pass
 
     def _submit_loop(self) -> None:
         while True:

@@ -21,16 +21,23 @@ from ..tp import get_tp, divide
 class KVCache:
     """[batch, capacity, 3*local_hidden] buffer holding, per token, this rank's key | value |
     query projection (the reference caches the three projections too, attention.py:86-98,
-    growing them with torch.cat).  Capacity grows geometrically; appends are written in place
-    by the QKV GEMM epilogue."""
+    growing them with torch.cat).  `reserve` is the number of generation steps the caller
+    announced: the prompt pass sizes the buffer for prompt + reserve positions, so that steps
+    replayed from a captured graph (which cannot reallocate) always find room; appends are
+    written in place by the QKV GEMM epilogue."""
 
     def __init__(self, reserve=256):
         self.buf, self.len, self.reserve = None, 0, reserve
 
-    def ensure(self, batch, need, width, dtype, device):
+    def capacity(self):
+        return 0 if self.buf is None else self.buf.shape[1]
+
+    def ensure(self, batch, need, width, dtype, device, exact=False):
+        """Room for `need` positions (exact: allocate just that; else `reserve` more, so that
+        eager appends do not reallocate every step).  Existing rows are kept."""
         if self.buf is not None and self.buf.shape[0] == batch and self.buf.shape[1] >= need and self.buf.dtype == dtype:
             return
-        cap = need + self.reserve
+        cap = need if exact else need + self.reserve
         new = torch.empty((batch, cap, width), dtype=dtype, device=device)
         if self.buf is not None and self.buf.shape[0] == batch and self.len > 0 and self.buf.dtype == dtype:
             new[:, :self.len] = self.buf[:, :self.len]
@@ -116,7 +123,9 @@ class MultiHeadAttention1D(nn.Module):
                 buf = torch.empty((B, S, 3 * hl), dtype=x.dtype, device=x.device)
             else:
                 cache.reset()
-                cache.ensure(B, S, 3 * hl, x.dtype, x.device)
+                # room for the announced generation steps too: a buffer kept from an earlier call
+                # is reused only if it holds the whole of this one
+                cache.ensure(B, S + max(0, cache.reserve), 3 * hl, x.dtype, x.device, exact=True)
                 buf = cache.buf
             gemm(x, w, bias=b, static_weight=True, out=buf, out_rows_per_batch=S, out_batch_stride=buf.stride(0), out_ld=buf.stride(1))
             kv_len = S
@@ -145,6 +154,8 @@ class MultiHeadAttention1D(nn.Module):
             else:
                 buf = cache.buf
                 cap = buf.shape[1]
+                if buf.shape[0] != B:
+                    raise RuntimeError("attention: the cache was sized for another batch")
                 gemm(x, w, bias=b, static_weight=True, out=buf, out_rows_per_batch=1, out_batch_stride=buf.stride(0), out_ld=buf.stride(1),
                      out_row_offset_device=kv_state[0:1], ln_fold=fold)
                 ctx = attention_decode(buf[:, :, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, cap, mask=mask,

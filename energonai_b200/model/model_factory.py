@@ -228,6 +228,10 @@ class PipelineModel(nn.Module):
             return input_ids
 
         # ---- generation steps ----
+        for blk in self.blocks:
+            # steps driven by device-side positions cannot grow the cache: it must hold the whole call
+            if not self.disable_past_cache and blk.attn.past_cache.capacity() < tgt_len:
+                raise RuntimeError(f"key/value cache holds {blk.attn.past_cache.capacity()} positions, {tgt_len} needed")
         st = self._graph_state(batch_size, tgt_len, model_dtype, dev, input_ids.dtype)
         st["add_mask"].zero_()
         st["add_mask"][:, :cur_len] = add_mask_prompt

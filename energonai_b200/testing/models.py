@@ -48,10 +48,23 @@ def expected_new_tokens(seed, steps):
 class FlakyModel(nn.Module):
     """4x + 1 like BoringModel at tensor-parallel size 1, except for two marker inputs: a first
     element of -1 raises (a request the model rejects), a first element of -2 ends the worker
-    process at once (a crashed worker).  Used to test what the engine tells its callers."""
+    process at once (a crashed worker).  A first element of -3 makes `health()` report a fault
+    from then on, which is how a worker learns that a bounded device-side wait ran out (made on
+    the host here; no GPU is involved).  Used to test what the engine tells its callers."""
+
+    def __init__(self, fail_at_start: bool = False) -> None:
+        super().__init__()
+        if fail_at_start:
+            raise RuntimeError("model_fn failed on purpose")
+        self.fault = None
+
+    def health(self):
+        return self.fault
 
     def forward(self, x):
         marker = float(x.reshape(-1)[0])
+        if marker == -3.0:
+            self.fault = "a wait on a tensor-parallel peer ran out (made up by the test)"
         if marker == -1.0:
             raise ValueError("request rejected by the model")
         if marker == -2.0:

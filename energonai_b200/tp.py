@@ -24,6 +24,14 @@ class TPContext:
             self.peer = PeerExchange(self.group, self.rank, self.world_size, max_rows, max_cols)
         return self.peer
 
+    def enable_peer_exchange_for(self, model, max_rows=128):
+        """enable_peer_exchange sized for `model`: the widest row-parallel output it contains."""
+        from .nn import Linear1D_Row
+        cols = [m.out_features for m in model.modules() if isinstance(m, Linear1D_Row)]
+        if self.world_size <= 1 or not cols:
+            return None
+        return self.enable_peer_exchange(max_rows, max(cols))
+
     def all_reduce(self, t):
         """In-place SUM over the tensor-parallel group (no-op for one rank)."""
         if self.world_size > 1:

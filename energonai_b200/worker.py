@@ -39,15 +39,28 @@ class Worker:
             torch.cuda.set_device(rank % n_proc_per_node)
         os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = master_host, str(master_port)
         dist.init_process_group("nccl" if use_cuda else "gloo", rank=rank, world_size=self.world_size)
-        tp.init_tp(tp_world_size)
-        model = model_fn(**model_kwargs)
-        self.model = model.cuda() if use_cuda else model
+        ctx = tp.init_tp(tp_world_size)
         self.device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
         self.rpc_name = f"worker{rank}"
+        # The RPC layer comes up before the model is built, so that a model_fn that raises can be
+        # reported to the master instead of leaving it waiting for a peer that never joins.
         trpc.init_rpc(self.rpc_name, rank=rank + 1, world_size=self.world_size + 1,
                       rpc_backend_options=rpc_options(master_host, rpc_port, rpc_disable_shm))
         self.input_pipe = Pipe(f"m_to_{rank}", "master", self.rpc_name, max_size=pipe_size)
         self.output_pipe = Pipe(f"{rank}_to_m", self.rpc_name, "master")
+        self.poisoned = None                           # set once the device reported a failed wait
+        try:
+            model = model_fn(**model_kwargs)
+            self.model = model.cuda() if use_cuda else model
+            if use_cuda and tp_world_size > 1:
+                # generation steps exchange their row-parallel partial sums over NVLink peer
+                # memory inside the GEMM kernels; NCCL remains for everything larger
+                ctx.enable_peer_exchange_for(self.model)
+        except Exception as exc:                       # noqa: BLE001 (sent to the master)
+            self.output_pipe.send(RemoteFailure(rank, f"{type(exc).__name__}: {exc}"))
+            _stop.wait(10.0)                           # the master tears the RPC layer down
+            trpc.shutdown(graceful=False)
+            return
         self.output_pipe.send(0)                       # announce: pipeline rank of this worker
         self._serve()
 
@@ -68,6 +81,20 @@ class Worker:
             return self.model(**inputs)
         return self.model(inputs)
 
+    def _health(self):
+        """None, or why this worker must not serve any more.  The kernels' waits (on tensor-core
+        pipelines and on the flags of tensor-parallel peers) are bounded: when one runs out, the
+        kernel records it in a device status word and returns, and the outputs of that call, and
+        the exchange buffers from then on, cannot be trusted.  A model may add its own check by
+        exposing `health()` (None or a message)."""
+        if self.device.type == "cuda":
+            from .gemm import device_status
+            code, where, block, detail = device_status(clear=True)
+            if code != 0:
+                return f"device status {code} (wait site {where}, block {block}, detail {detail})"
+        probe = getattr(self.model, "health", None)
+        return probe() if callable(probe) else None
+
     def _serve(self) -> None:
         try:
             while not _stop.is_set():
@@ -76,9 +103,14 @@ class Worker:
                 except RuntimeError:
                     continue
                 try:
+                    if self.poisoned is not None:
+                        raise RuntimeError(f"worker {self.global_rank} stopped serving after: {self.poisoned}")
                     with torch.inference_mode():
                         out = self._forward(task.batch)
-                    out = out.cpu() if torch.is_tensor(out) else out
+                    out = out.cpu() if torch.is_tensor(out) else out   # (synchronises the device)
+                    self.poisoned = self._health()
+                    if self.poisoned is not None:
+                        raise RuntimeError(self.poisoned)
                 except Exception as exc:                 # answer the batch with the error, keep serving
                     out = RemoteFailure(self.global_rank, f"{type(exc).__name__}: {exc}")
                 self.output_pipe.send(TaskEntry(task.uids, out))

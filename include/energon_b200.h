@@ -291,8 +291,10 @@ EB_API size_t eb_attention_decode_scratch_bytes(int batch, int heads, int head_d
  * each device looks the array's address up and clears its counters on `stream`; make that
  * first call outside any stream capture.  All calls on a device share the one array and it
  * keeps the previous call's contents, so calls that overlap on the GPU (two streams, two
- * threads) race: serialise them.  Nothing is allocated or freed.  No counterpart in the
- * reference. */
+ * threads) race: serialise them, the first call per device included (the address look-up is
+ * guarded against concurrent host threads, but the clearing of the counters is ordered only
+ * on the stream of the call that does it).  A request with nsplit 1 uses no scratch and skips
+ * all of this.  Nothing is allocated or freed.  No counterpart in the reference. */
 EB_API int eb_attention_decode_noalloc(const void *q, const void *k, const void *v, void *out, const void *mask,
                                 long long q_batch_stride, long long q_row_stride, long long k_batch_stride,
                                 long long k_row_stride, long long v_batch_stride, long long v_row_stride,

@@ -1,7 +1,7 @@
 """One engine life cycle in a fresh process (torch RPC cannot be re-initialised reliably inside
 one process, which is also why the reference runs its engine tests one file per process):
 
-    python -m energonai_b200.testing.engine_check <tp_world_size> [generation|failure]
+    python tests/engine_check.py <tp_world_size> [generation|failure|unhealthy|startup]
 
 Launches workers, submits requests through a batching manager, checks BoringModel's closed form
 (4x + 1), checks QueueFullError, shuts down.  With `generation`, the engine runs
@@ -132,9 +132,48 @@ def main_failure():
     print("engine failure ok", flush=True)
 
 
+def main_unhealthy():
+    """A worker whose health check reports a fault answers that batch, and every later one, with
+    an error instead of results it cannot vouch for."""
+    from energonai_b200.testing.models import FlakyModel
+    engine = launch_engine(1, 1, "127.0.0.1", free_port(), free_port(), FlakyModel)
+    try:
+        engine.submit("ok", torch.ones(4))
+        assert torch.equal(engine.get("ok"), get_correct_output(torch.ones(4)))
+        for uid, x in (("faulted", torch.full((4,), -3.0)), ("later", torch.ones(4))):
+            engine.submit(uid, x)
+            try:
+                engine.get(uid)
+                raise AssertionError(f"{uid}: a faulted worker must not return results")
+            except RuntimeError as exc:
+                assert "ran out" in str(exc), exc
+    finally:
+        engine.shutdown()
+    print("engine unhealthy ok", flush=True)
+
+
+def main_startup():
+    """A model_fn that raises makes launch_engine raise instead of waiting forever."""
+    import time
+    from energonai_b200 import WorkerFailedError
+    from energonai_b200.testing.models import FlakyModel
+    t0 = time.time()
+    try:
+        launch_engine(1, 1, "127.0.0.1", free_port(), free_port(), FlakyModel, fail_at_start=True)
+        raise AssertionError("launch_engine must raise when a worker cannot start")
+    except WorkerFailedError as exc:
+        assert "failed on purpose" in str(exc) or "during start-up" in str(exc), exc
+    assert time.time() - t0 < 60
+    print("engine startup ok", flush=True)
+
+
 if __name__ == "__main__":
     if len(sys.argv) > 2 and sys.argv[2] == "failure":
         main_failure()
+    elif len(sys.argv) > 2 and sys.argv[2] == "unhealthy":
+        main_unhealthy()
+    elif len(sys.argv) > 2 and sys.argv[2] == "startup":
+        main_startup()
     elif len(sys.argv) > 2 and sys.argv[2] == "generation":
         main_generation(int(sys.argv[1]))
     else:

@@ -1,6 +1,6 @@
 """One engine life cycle on a GPU in a fresh process:
 
-    python -m energonai_b200.testing.engine_check_gpu
+    python tests/engine_check_gpu.py
 
 launch_engine starts one worker on cuda:0 that builds a small OPT-shaped PipelineModel (seeded);
 generation requests (input_ids, attention_mask, max_tokens, top_k=1) travel through the RPC

@@ -1,5 +1,5 @@
 """launch_engine with a GPU worker: generation requests through the RPC pipes return the tokens
-the model produces when called directly (energonai_b200/testing/engine_check_gpu.py; its own
+the model produces when called directly (tests/engine_check_gpu.py; its own
 process because torch RPC cannot be re-initialised inside one)."""
 import os
 import subprocess
@@ -14,6 +14,6 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_engine_generation_on_gpu():
     env = dict(os.environ, PYTHONPATH=ROOT, MASTER_ADDR="127.0.0.1")
-    r = subprocess.run([sys.executable, "-m", "energonai_b200.testing.engine_check_gpu"], cwd=ROOT, env=env,
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "engine_check_gpu.py")], cwd=ROOT, env=env,
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "engine gpu ok" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]

@@ -137,6 +137,11 @@ def compare_tokens(tokens, gold, margin_tol=2e-2):
     return exact
 
 
+def count_ties(gold, margin_tol=2e-2):
+    """Sequences with at least one step whose reference fp32 top-2 margin is a numerical tie."""
+    return int((gold["top2_margin"] < margin_tol).any(0).sum())
+
+
 def test_tiny_generation_tokens_and_hidden():
     tokens, gold, rec = run_generation(mg.TINY, 7, "opt_tiny_generate.npz")
     exact = compare_tokens(tokens, gold)
@@ -151,7 +156,9 @@ def test_cfg1_opt125m_greedy_tokens():
     tokens, gold, _ = run_generation(mg.CFG1, 0, "cfg1_opt125m_generate.npz")
     exact = compare_tokens(tokens, gold)
     print(f"cfg1: {exact}/{tokens.shape[0]} sequences identical over 32 steps")
-    assert exact >= tokens.shape[0] // 2
+    # every sequence must be identical; one may differ only from a step on where the reference's
+    # own fp32 margin is a numerical tie (compare_tokens has verified that for each divergence)
+    assert exact >= tokens.shape[0] - count_ties(gold)
 
 
 def test_sampling_path_runs():
@@ -187,3 +194,69 @@ def test_graph_replayed_generation_equals_eager():
     out_eager = model(input_ids=ids, attention_mask=mask, max_tokens=30, top_k=1)
     assert out_graph.shape == (3, 30)
     assert torch.equal(out_graph, out_eager) and torch.equal(out_graph, out_again)
+
+
+CFG3_LAYER = dict(vocab=2048, max_pos=128, hidden=5120, heads=40, ffn=20480, depth=2, B=16, S=64, new=6)
+
+
+def test_config3_layer_shape_eager_and_replayed_steps_against_oracle():
+    """Two layers of BASELINE configuration 3's exact shape (hidden 5120, 40 heads of 128, FFN
+    20480, ReLU, unfused QKV, fp16, batch 16, left-padded prompts), prompt length and vocabulary
+    reduced so that the CPU oracle finishes in seconds.  The generation steps run with the
+    LayerNorms folded into the projections; they are checked eagerly (final-norm hidden state and
+    fp32 logits of every step, element-wise against the oracle) and replayed from the captured
+    graph (tokens identical to the eager run)."""
+    from energonai_b200.model import create_pipeline_model
+    c = CFG3_LAYER
+    p = inputs.model_params(3, c["vocab"], c["max_pos"], c["hidden"], c["ffn"], c["depth"], rich=True)
+    ids, mask, _ = inputs.left_padded_prompts(3, c["B"], c["S"], c["S"] // 2, c["S"], c["vocab"])
+    tgt = c["S"] + c["new"]
+    ref_rec = {}
+    with torch.inference_mode():
+        ref_out = layers.OracleModel(p, c["depth"], c["heads"], "relu").generate(ids, mask, tgt, ref_rec)
+    model = create_pipeline_model(depth=c["depth"], vocab_size=c["vocab"], hidden_size=c["hidden"], max_seq_len=c["max_pos"],
+                                  num_heads=c["heads"], mlp_ratio=c["ffn"] / c["hidden"], activation=torch.nn.functional.relu,
+                                  is_decoder=True, fused_qkv=False, dtype=torch.float16)
+    model.load_state_dict({k: v.half() for k, v in layers.model_to_reference_state(p, c["depth"], False).items()}, strict=True)
+    assert model.blocks[0].fold_layernorm
+    rec = {}
+    eager = model(input_ids=ids.cuda(), attention_mask=mask.cuda(), max_tokens=tgt, top_k=1, record=rec)
+    assert model._decode_state["graph"] is None
+    ref_logits = torch.stack(ref_rec["logits"], 0)
+    top2 = ref_logits.topk(2, -1).values
+    gold = {"tokens": ref_out[:, c["S"]:].numpy(), "top2_margin": (top2[..., 0] - top2[..., 1]).numpy()}
+    exact = compare_tokens(eager[:, c["S"]:].cpu().numpy(), gold)
+    if exact == c["B"]:     # same tokens fed at every step: the per-step activations are comparable
+        assert_close(torch.stack(rec["hidden"], 0), torch.stack(ref_rec["hidden"], 0), "final-norm hidden state")
+        assert_close(torch.stack(rec["logits"], 0), ref_logits, "fp32 logits")
+    replayed = model(input_ids=ids.cuda(), attention_mask=mask.cuda(), max_tokens=tgt, top_k=1)
+    assert model._decode_state["graph"] is not None
+    assert torch.equal(replayed, eager)
+    from energonai_b200.gemm import device_status
+    assert device_status()[0] == 0
+
+
+def test_second_call_with_shorter_prompt_and_more_tokens_gets_a_large_enough_cache():
+    """A model instance serves requests of different lengths: the second call has a shorter
+    prompt but asks for more positions than the first call's cache held.  The replayed steps
+    write cache rows by device-side position, so the prompt pass must have sized the cache for
+    the whole call; the tokens must equal those of the eager path on a fresh model."""
+    from energonai_b200.model import create_pipeline_model
+    c = mg.TINY
+
+    def make():
+        torch.manual_seed(3)
+        return create_pipeline_model(depth=2, vocab_size=c["vocab"], hidden_size=c["hidden"], max_seq_len=128,
+                                     num_heads=c["heads"], activation=torch.nn.functional.relu, fused_qkv=False,
+                                     dtype=torch.float16)
+    a = make()
+    ids1 = torch.randint(2, c["vocab"], (2, 20), device="cuda")
+    ids2 = torch.randint(2, c["vocab"], (2, 10), device="cuda")
+    a(input_ids=ids1, attention_mask=torch.ones(2, 20, device="cuda"), max_tokens=50, top_k=1)
+    cap1 = a.blocks[0].attn.past_cache.capacity()
+    out_a = a(input_ids=ids2, attention_mask=torch.ones(2, 10, device="cuda"), max_tokens=110, top_k=1)
+    assert cap1 < 110 <= a.blocks[0].attn.past_cache.capacity()
+    b = make()
+    b.use_cuda_graph = False
+    out_b = b(input_ids=ids2, attention_mask=torch.ones(2, 10, device="cuda"), max_tokens=110, top_k=1)
+    assert out_a.shape == (2, 110) and torch.equal(out_a, out_b)
