@@ -9,11 +9,17 @@ model sharded over N GPUs (tensor parallel, heads and FFN columns).  Rank 0 prin
 line.  Inputs are synthetic and weights random-init (seeded); the weights alone (26 GB) are
 larger than L2, so consecutive timed steps cannot reuse cached data.
 
+Besides timing, the run verifies what it timed (outside the timed region): all ranks must
+hold identical tokens, no bounded device-side wait may have run out, and a two-layer model of
+the same layer shape, sharded the same way, must reproduce the CPU oracle's greedy tokens and
+final hidden states ("check" in the line).
+
 `--impl reference` times the reference's own algorithm for this path (its PyTorch layer
 forward, restated in oracle/layers.py) on the host CPU cores, on a bounded sample of the
 same workload, and prints the same line with "impl": "reference".
 """
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -35,8 +41,9 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return {"hbm": float(d["hbm_gbs"]), "tensor": float(d["bf16_tflops"]),
+                "tensor_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "kind": "measured"}
+    return {"hbm": 6650.0, "tensor": 1590.0, "tensor_sustained": 1400.0, "kind": "fallback"}
 
 
 class ClockSampler:
@@ -147,44 +154,84 @@ def workload_config(n_gpus):
 # ------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------
-def build_model(cfg, dtype):
+def build_model(cfg, dtype, world):
     import torch
     from energonai_b200.model import create_pipeline_model
     torch.manual_seed(1234)          # same seed on every rank: replicated parameters agree
     with torch.device("cuda"):
+        # on a tensor-parallel group the vocabulary is split too (the reference does that for its
+        # largest factory, model_factory.py:352): every rank streams 1/N of the LM head per step
         model = create_pipeline_model(depth=cfg["depth"], vocab_size=cfg["vocab"], hidden_size=cfg["hidden"],
                                       max_seq_len=cfg["max_pos"], num_heads=cfg["heads"],
                                       mlp_ratio=cfg["ffn"] / cfg["hidden"], activation=torch.nn.functional.relu,
-                                      is_decoder=True, fused_qkv=False, dtype=dtype)
+                                      is_decoder=True, fused_qkv=False, dtype=dtype, vocab_parallel=world > 1)
     with torch.no_grad():
         model.embed.word_embeddings.weight.normal_(0, 0.02)
         model.embed.position_embeddings.weight.normal_(0, 0.02)
     return model.eval()
 
 
-def probe_decode_gemms(model, cfg):
-    """Average device time per launch of the generation-step GEMM (the dominant kernel).
+def step_bytes(cfg, world, kv_len):
+    """Algorithmic bytes one generation step moves on ONE rank: this rank's weight shards, its
+    slice of the cached keys and values, the LM head it streams."""
+    h, f, e = cfg["hidden"], cfg["ffn"], 2
+    weights = cfg["depth"] * (4 * h * h + 2 * h * f) * e / world
+    kv = cfg["depth"] * 2 * cfg["batch"] * kv_len * h * e / world
+    head = cfg["vocab"] * h * e / world
+    return weights + kv + head
 
-    All four GEMMs of every layer are launched back to back, with each layer's own weights (so
-    every launch streams weights that are not in L2), captured in one CUDA graph and replayed;
-    CUDA events on the launching stream bracket each replay.  Returns (algorithmic bytes, ms,
-    launches) per replay."""
+
+def probe_decode_kernels(model, cfg, st, world):
+    """Average device time per launch of the dominant generation-step kernel, launched with the
+    step's real arguments (folded LayerNorms, bias, residual, cache-row mapping, the exchange of
+    a tensor-parallel group), back to back, each layer on its own weights (nothing is
+    L2-resident), captured in one CUDA graph and replayed between CUDA events.
+
+    Single rank: the four GEMMs of every layer (eb_gemm_ln for QKV / FC1, eb_gemm with bias and
+    residual for out-proj / FC2).  Tensor-parallel group: the chained launches of the step (one
+    per layer: out-proj, exchange, FC1, FC2, exchange, QKV).  Returns a dict."""
     import torch
-    from energonai_b200.gemm import gemm
     B, h = cfg["batch"], cfg["hidden"]
     dt = model.norm.module.weight.dtype
-    x = torch.randn(B, h, device="cuda", dtype=dt)
-    jobs = []
-    for blk in model.blocks:
-        w_qkv, _ = blk.attn._packed()
-        jobs += [(x, w_qkv), (torch.randn(B, blk.attn.dense.weight.shape[1], device="cuda", dtype=dt), blk.attn.dense.weight),
-                 (x, blk.mlp.dense_1.weight),
-                 (torch.randn(B, blk.mlp.dense_2.weight.shape[1], device="cuda", dtype=dt), blk.mlp.dense_2.weight)]
+    e = 2
+    if st.get("chains"):
+        chains = st["chains"]
 
-    def run():
-        for a, w in jobs:
-            gemm(a, w, static_weight=True)
+        def run():
+            for ch in chains:
+                ch.run()
+        n_launch = len(chains)
+        nbytes = cfg["depth"] * (4 * h * h + 2 * h * cfg["ffn"]) * e / world + cfg["vocab"] * h * e / world
+        name = "chain_kernel<__half, 16> (one launch per layer: out-proj, exchange + LayerNorm, FC1, FC2, exchange + LayerNorm, QKV)"
+    else:
+        from energonai_b200.gemm import gemm
+        x = torch.randn(B, 1, h, device="cuda", dtype=dt)
+        kv_state = st["kv_state"]
+        jobs = []
+        nbytes = 0
+        for blk in model.blocks:
+            at, mlp = blk.attn, blk.mlp
+            w, b = at._packed()
+            w_f, colsum, bias32, eps = at._fold.get(w, b, blk.norm1, at._param_versions())
+            buf = at.past_cache.buf
+            ctx = torch.randn(B, 1, at.local_hidden, device="cuda", dtype=dt)
+            jobs.append(lambda w_f=w_f, colsum=colsum, bias32=bias32, eps=eps, buf=buf: gemm(
+                x[:, 0], w_f, static_weight=True, out=buf, out_rows_per_batch=1, out_batch_stride=buf.stride(0),
+                out_ld=buf.stride(1), out_row_offset_device=kv_state[0:1], out_row_limit=buf.shape[1],
+                ln_fold=(colsum, bias32, eps)))
+            jobs.append(lambda at=at, ctx=ctx: at.dense(ctx, residual=x))
+            jobs.append(lambda mlp=mlp, blk=blk: mlp.dense_1(x, act=mlp.act_code, fold_norm=blk.norm2))
+            inter = torch.randn(B, 1, mlp.dense_1.out_per_rank, device="cuda", dtype=dt)
+            jobs.append(lambda mlp=mlp, inter=inter: mlp.dense_2(inter, residual=x))
+            for wt, k_in in ((w, h), (at.dense.weight, at.local_hidden), (mlp.dense_1.weight, h),
+                             (mlp.dense_2.weight, mlp.dense_1.out_per_rank)):
+                nbytes += (wt.numel() + B * k_in + B * wt.shape[0]) * e
 
+        def run():
+            for j in jobs:
+                j()
+        n_launch = len(jobs)
+        name = "gemm_kernel<__half, 16, true> (generation-step GEMM, M = batch 16; QKV / FC1 with the LayerNorm folded in)"
     run()
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
@@ -199,37 +246,151 @@ def probe_decode_gemms(model, cfg):
         g.replay()
     e1.record()
     torch.cuda.synchronize()
-    nbytes = sum((w.shape[0] * w.shape[1] + a.shape[0] * a.shape[1] + a.shape[0] * w.shape[0]) * 2 for a, w in jobs)
-    return nbytes, e0.elapsed_time(e1) / reps, len(jobs)
+    ms = e0.elapsed_time(e1) / reps
+    return {"kernel": name, "bytes": nbytes, "ms": ms, "launches": n_launch}
+
+
+def exposed_exchange(model, cfg, ids_d, mask_d, tgt, prefill_ms, step_ms):
+    """How much of the prompt pass and of the generation step is spent waiting for the other
+    ranks: the same shards, shapes and launches are timed once more with the exchange reduced to
+    this rank alone (a context of one rank that exchanges with itself; NCCL all-reduces skipped),
+    so the numbers it produces are meaningless but nothing waits for a peer.
+    exposed fraction = (time with the exchange - time without) / time with."""
+    import torch
+    from energonai_b200 import tp
+    from energonai_b200.comm import PeerExchange
+    ctx = tp.get_tp()
+    real_peer, real_all_reduce, real_gather = ctx.peer, ctx.all_reduce, ctx.all_gather_last_dim
+    area = torch.zeros(real_peer.recv_bytes if real_peer is not None else 1 << 20, dtype=torch.uint8, device="cuda")
+    solo = PeerExchange.from_pointers(0, 1, area, [area.data_ptr()])
+    solo.max_rows, solo.max_cols = cfg["batch"], cfg["hidden"]
+    saved_state = model._decode_state
+    try:
+        if real_peer is not None:
+            ctx.peer = solo
+        ctx.all_reduce = lambda t: t
+        ctx.all_gather_last_dim = lambda t: torch.cat([t] * ctx.world_size, dim=-1)
+        model._decode_state = None
+        rec = {"allow_graph": True}
+        model(input_ids=ids_d, attention_mask=mask_d, max_tokens=tgt, top_k=1, record=rec)
+        model(input_ids=ids_d, attention_mask=mask_d, max_tokens=tgt, top_k=1, record=(rec := {"allow_graph": True}))
+        torch.cuda.synchronize()
+        ev = rec["step_events"]
+        solo_prefill = ev[0].elapsed_time(ev[1])
+        solo_steps = [a.elapsed_time(b) for a, b in zip(ev[1:-1], ev[2:])]
+    finally:
+        ctx.peer, ctx.all_reduce, ctx.all_gather_last_dim = real_peer, real_all_reduce, real_gather
+        model._decode_state = saved_state
+        from energonai_b200.gemm import device_status
+        device_status(clear=True)
+        solo.destroy()
+    solo_step = statistics.median(solo_steps) if solo_steps else None
+    out = {"prefill_ms_without_exchange": solo_prefill, "decode_step_ms_without_exchange": solo_step,
+           "exposed_allreduce_frac_prefill": max(0.0, (prefill_ms - solo_prefill) / prefill_ms)}
+    if solo_step and step_ms:
+        out["exposed_allreduce_frac_decode"] = max(0.0, (step_ms - solo_step) / step_ms)
+    return out
+
+
+def verify(world, rank, out_tokens):
+    """Checks on what was timed, outside the timed region.  Returns a dict for the line."""
+    import torch
+    import torch.distributed as dist
+    from energonai_b200 import tp
+    from energonai_b200.gemm import device_status
+    from energonai_b200.sharding import shard_model_state
+    from oracle import inputs, layers      # the checker (never on the timed path)
+    res = {}
+    problems = []
+    tok = out_tokens.contiguous()
+    res["tokens_sha"] = hashlib.sha256(tok.cpu().numpy().tobytes()).hexdigest()[:16]
+    if world > 1:
+        gathered = [torch.empty_like(tok) for _ in range(world)]
+        dist.all_gather(gathered, tok)
+        if not all(torch.equal(gathered[0], t) for t in gathered):
+            problems.append("ranks hold different tokens")
+    st = device_status(clear=True)
+    peer = tp.get_tp().peer
+    cst = peer.status() if peer is not None else (0, 0, 0, 0)
+    bad = torch.tensor([1.0 if (st[0] != 0 or cst[0] != 0) else 0.0], device="cuda")
+    if world > 1:
+        dist.all_reduce(bad)
+    if float(bad) > 0:
+        problems.append(f"a device-side wait ran out or a limit was hit on some rank (this rank: {st}, {cst})")
+
+    # two layers of the benchmark's layer shape, sharded like the benchmark, against the CPU oracle
+    c = dict(vocab=2048, max_pos=128, hidden=CFG["hidden"], heads=CFG["heads"], ffn=CFG["ffn"], depth=2, B=CFG["batch"], S=32, new=5)
+    from energonai_b200.model import PipelineModel
+    p = inputs.model_params(3, c["vocab"], c["max_pos"], c["hidden"], c["ffn"], c["depth"], rich=True)
+    ids, mask, _ = inputs.left_padded_prompts(3, c["B"], c["S"], c["S"] // 2, c["S"], c["vocab"])
+    tgt = c["S"] + c["new"]
+    full = {k: v.half() for k, v in layers.model_to_reference_state(p, c["depth"], False).items()}
+    with torch.device("cuda"):
+        small = PipelineModel(vocab_size=c["vocab"], max_seq_len=c["max_pos"], hidden_size=c["hidden"], num_heads=c["heads"],
+                              depth=c["depth"], mlp_ratio=c["ffn"] / c["hidden"], activation=torch.nn.functional.relu,
+                              dtype=torch.float16, fused_qkv=False, vocab_parallel=world > 1).eval()
+    small.load_state_dict(shard_model_state(full, rank, world, vocab_parallel=world > 1), strict=True)
+    del full
+    got = small(input_ids=ids.cuda(), attention_mask=mask.cuda(), max_tokens=tgt, top_k=1)      # replayed steps
+    res["check_step_launch"] = (small._decode_state or {}).get("chain_mode") or "one kernel per operation"
+    if rank == 0:
+        rec = {}
+        with torch.inference_mode():
+            want = layers.OracleModel(p, c["depth"], c["heads"], "relu").generate(ids, mask, tgt, rec)
+        logits = torch.stack(rec["logits"], 0)
+        top2 = logits.topk(2, -1).values
+        margin = (top2[..., 0] - top2[..., 1])              # [new, B]
+        got_c, ok_seqs = got.cpu(), 0
+        for b in range(c["B"]):
+            diff = (got_c[b, c["S"]:] != want[b, c["S"]:]).nonzero()
+            if diff.numel() == 0:
+                ok_seqs += 1
+            elif float(margin[int(diff[0]), b]) >= 2e-2:
+                problems.append(f"sequence {b} leaves the oracle's greedy tokens at step {int(diff[0])} "
+                                f"(margin {float(margin[int(diff[0]), b]):.3g})")
+        res["check_sequences_identical"] = f"{ok_seqs}/{c['B']}"
+    st = device_status(clear=True)
+    if st[0] != 0:
+        problems.append(f"device status after the check run: {st}")
+    del small
+    torch.cuda.empty_cache()
+    flag = torch.tensor([float(len(problems))], device="cuda")
+    if world > 1:
+        dist.all_reduce(flag)
+    res["check"] = "ok" if float(flag) == 0 else "FAILED: " + "; ".join(problems or ["see another rank"])
+    return res
 
 
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from energonai_b200 import _lib, tp
-    from oracle import inputs   # seeded prompt generator only (no oracle compute on this path)
+    from energonai_b200 import tp
+    from oracle import inputs   # seeded prompt generator only (no oracle compute on the timed path)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        ctx = tp.init_tp(world)
-        if os.environ.get("EB_PEER", "1") != "0":
-            # generation steps: all-reduce fused into the row-parallel GEMM epilogue (NVLink peer stores)
-            try:
-                ctx.enable_peer_exchange(CFG["batch"], CFG["hidden"])
-            except Exception as e:          # no peer mapping on this box: NCCL carries every all-reduce
-                ctx.peer = None
-                if rank == 0:
-                    print(f"peer exchange unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
     cfg = dict(CFG)
     if args.layers:
         cfg["depth"] = args.layers
     if args.new_tokens:
         cfg["new_tokens"] = args.new_tokens
-    model = build_model(cfg, torch.float16)
+    exchange_kind = "none (one rank)"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        ctx = tp.init_tp(world)
+        exchange_kind = "NCCL all-reduce"
+        if os.environ.get("EB_PEER", "1") != "0":
+            # generation steps: the all-reduces run inside the library's own kernels over NVLink peer memory
+            try:
+                ctx.enable_peer_exchange(128, cfg["hidden"])
+                exchange_kind = "prompt pass: NCCL all-reduce; generation steps: inside the chained kernel, NVLink peer stores"
+            except Exception as e:          # no peer mapping on this box: NCCL carries every all-reduce
+                ctx.peer = None
+                if rank == 0:
+                    print(f"peer exchange unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+    model = build_model(cfg, torch.float16, world)
     ids_h, mask_h, _ = inputs.left_padded_prompts(0, cfg["batch"], cfg["prompt"], cfg["len_lo"], cfg["prompt"], cfg["vocab"])
     ids_h, mask_h = ids_h.pin_memory(), mask_h.pin_memory()
     ids_d, mask_d = ids_h.cuda(), mask_h.cuda()
@@ -272,36 +433,33 @@ def run_ours(args):
     # the same metric end to end: host (pinned) inputs in, host tokens out, copies inside the timed region
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_wall = time.perf_counter()
     e0.record()
     for _ in range(args.steps):
         out_h = one(False)
     e1.record()
     barrier()
-    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t_wall) * 1e3 * 0)   # device time; the .cpu() read is synchronous
+    e2e_ms = e0.elapsed_time(e1)          # device time; the .cpu() read of the tokens is synchronous
 
     if world > 1:
         t = torch.tensor([elapsed_ms, e2e_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms, e2e_ms = t.tolist()
 
-    # per-phase figures from the step events of the timed region (rank 0's own clock)
+    # per-phase figures from the step events of the timed region (this rank's own clock)
     prefill_ms, step_ms = [], []
     for rec in recs:
         ev = rec["step_events"]
         prefill_ms.append(ev[0].elapsed_time(ev[1]))
         step_ms += [a.elapsed_time(b) for a, b in zip(ev[1:-1], ev[2:])]
-    peak, peak_kind = measured_peaks()
-    roof = None
-    if rank == 0 or world > 1:
-        gemm_bytes, gemm_ms, gemm_n = probe_decode_gemms(model, cfg)
-        achieved = gemm_bytes / (gemm_ms * 1e-3) / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                # dram__bytes_read+write per launch from the ncu capture summarised in
-                # profiles/gemm_decode_opt13b_m16.md (same four shapes, full-size launches)
-                "traffic": 162.0e6 if (world == 1 and not args.layers) else None, "kernel": "gemm_kernel<__half, 16, true> (generation-step GEMM, M = batch 16)",
-                "peak_kind": f"of {peak_kind}", "launches_timed": gemm_n,
-                "algorithmic_bytes_per_launch": gemm_bytes / max(1, gemm_n), "us_per_launch": gemm_ms * 1e3 / max(1, gemm_n)}
+    prefill_mean = statistics.mean(prefill_ms)
+    step_p50 = statistics.median(step_ms) if step_ms else None
+    peaks = measured_peaks()
+
+    # ---- explanations, outside the timed region ----
+    probe = probe_decode_kernels(model, cfg, model._decode_state, world)
+    exposed = exposed_exchange(model, cfg, ids_d, mask_d, tgt, prefill_mean, step_p50) if world > 1 else None
+    checks = verify(world, rank, out) if not args.no_check else {"check": "skipped"}
+
     def finish():
         # Captured graphs hold NCCL kernels; tearing the process group down under them can
         # block, so release the graphs, rendezvous once more and leave without the teardown.
@@ -316,19 +474,44 @@ def run_ours(args):
     if rank != 0:
         finish()
         return
+    achieved = probe["bytes"] / (probe["ms"] * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "decode_gemm_dram_bytes_per_launch.txt")
+    if world == 1 and not args.layers and os.path.exists(tpath):
+        with open(tpath) as f:            # dram__bytes_read.sum + dram__bytes_write.sum per launch, from an ncu capture
+            traffic = float(f.read().split()[0])
+    roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s", "frac": achieved / peaks["hbm"],
+            "traffic": traffic, "kernel": probe["kernel"], "peak_kind": f"of {peaks['kind']}",
+            "launches_timed": probe["launches"], "algorithmic_bytes_per_launch": probe["bytes"] / max(1, probe["launches"]),
+            "us_per_launch": probe["ms"] * 1e3 / max(1, probe["launches"])}
+    if step_p50:
+        kv_mid = cfg["prompt"] + cfg["new_tokens"] // 2
+        whole = step_bytes(cfg, world, kv_mid) / (step_p50 * 1e-3) / 1e9
+        roof["whole_step"] = {"algorithmic_bytes_per_rank": step_bytes(cfg, world, kv_mid), "achieved": whole, "frac": whole / peaks["hbm"],
+                              "note": "weights + keys/values + LM head of one rank / decode_step_ms_p50"}
+    h, f, T = cfg["hidden"], cfg["ffn"], cfg["batch"] * cfg["prompt"]
+    prompt_flops = cfg["depth"] * (2 * T * h * (4 * h + 2 * f) + 4 * cfg["batch"] * cfg["prompt"] ** 2 * h / 2) / world
+    roof["prompt_pass"] = {"bound": "tensor", "achieved": prompt_flops / (prefill_mean * 1e-3) / 1e12, "unit": "TFLOP/s",
+                           "peak": peaks["tensor_sustained"], "frac": prompt_flops / (prefill_mean * 1e-3) / 1e12 / peaks["tensor_sustained"],
+                           "note": "GEMM + causal-useful attention flops of one rank / prefill_ms, against the sustained bf16 GEMM peak"}
     ms_per_step = elapsed_ms / args.steps
     value = tokens_per_step / (ms_per_step * 1e-3)
+    config = workload_config(world)
+    config["exchange"] = exchange_kind
+    config["lm_head"] = "vocabulary split over the ranks" if world > 1 else "replicated"
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "fp16", "data": "synthetic", "config": workload_config(world),
-            "prefill_tokens_per_s": cfg["batch"] * cfg["prompt"] / (statistics.mean(prefill_ms) * 1e-3),
+            "vs_baseline": None, "dtype": "fp16", "data": "synthetic", "config": config,
+            "prefill_tokens_per_s": cfg["batch"] * cfg["prompt"] / (prefill_mean * 1e-3),
             "decode_tokens_per_s": cfg["batch"] / (statistics.mean(step_ms) * 1e-3) if step_ms else None,
-            "decode_step_ms_p50": statistics.median(step_ms) if step_ms else None,
-            "prefill_ms": statistics.mean(prefill_ms),
+            "decode_step_ms_p50": step_p50, "prefill_ms": prefill_mean,
             "e2e": {"value": tokens_per_step / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": ids_h.numel() * ids_h.element_size() + mask_h.numel() * mask_h.element_size(),
                     "d2h_bytes_per_step": out_h.numel() * out_h.element_size()},
             "gpu_launches": launches, "clocks": clocks, "roofline": roof}
+    line.update(checks)
+    if exposed:
+        line.update(exposed)
     if world == 1 and not args.no_cpu:
         v, sample, cores, _ = cpu_sample(CFG)
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
@@ -339,9 +522,6 @@ def run_ours(args):
 
 
 def main():
-    if os.environ.get("EB_BENCH_WATCHDOG"):       # debugging aid: dump all Python stacks if the run stalls
-        import faulthandler
-        faulthandler.dump_traceback_later(int(os.environ["EB_BENCH_WATCHDOG"]), repeat=False, exit=True)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
@@ -350,6 +530,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers (marks the line as reduced)")
     ap.add_argument("--new-tokens", type=int, default=0, help="debug: fewer generation steps (marks the line as reduced)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-check", action="store_true", help="skip the verification against the oracle")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -64,9 +64,9 @@ def last_error():
 launch_count = 0     # successful compute calls through the C ABI (each launches exactly one kernel)
 
 
-def check(rc, what=""):
+def check(rc, what="", launches=1):
     global launch_count
-    launch_count += 1
+    launch_count += launches
     if rc != 0:
         raise RuntimeError(f"energon_b200 {what} failed ({rc}): {last_error()}")
 

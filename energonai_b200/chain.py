@@ -7,7 +7,7 @@ import torch
 from ._lib import lib, check, dtype_code, stream_ptr, require_cuda
 from .gemm import ACT_CODES
 
-OP_GEMM, OP_LAYERNORM = 0, 1
+OP_GEMM, OP_LAYERNORM, OP_REDUCE_LAYERNORM = 0, 1, 2
 MAX_OPS = 8
 
 
@@ -21,6 +21,7 @@ class ChainOp(ctypes.Structure):
                 ("N", ctypes.c_int), ("K", ctypes.c_int), ("out_dtype", ctypes.c_int), ("act", ctypes.c_int),
                 ("c_rows_per_batch", ctypes.c_int), ("c_batch_stride", ctypes.c_longlong),
                 ("c_row_offset_device", ctypes.c_void_p),
+                ("c_row_offset_limit", ctypes.c_int), ("exchange", ctypes.c_int),
                 ("x", ctypes.c_void_p), ("y", ctypes.c_void_p), ("gamma", ctypes.c_void_p), ("beta", ctypes.c_void_p),
                 ("n2", ctypes.c_int), ("eps", ctypes.c_double)]
 
@@ -29,10 +30,23 @@ def _p(t):
     return None if t is None else t.data_ptr()
 
 
-def gemm_op(a, w, out, bias=None, residual=None, act=None, out_rows_per_batch=0, out_batch_stride=0, out_ld=None,
-            out_row_offset_device=None):
-    """C = act(a @ w.T + bias) + residual as one operation of a chain; arguments as gemm()."""
+def gemm_op(a, w, out=None, bias=None, residual=None, act=None, out_rows_per_batch=0, out_batch_stride=0, out_ld=None,
+            out_row_offset_device=None, out_row_limit=0, exchange=False):
+    """C = act(a @ w.T + bias) + residual as one operation of a chain; arguments as gemm().
+    exchange=True: `w` is this rank's column shard of a row-parallel layer; the product is sent
+    to the ranks of the chain's context instead of being stored (no out, bias, residual or act)
+    and the next operation must be reduce_layernorm_op()."""
     require_cuda(a, w, out, bias, residual, out_row_offset_device)
+    if exchange:
+        if out is not None or bias is not None or residual is not None or act not in (None, "none", 0):
+            raise RuntimeError("chain gemm: an exchanged product takes no out, bias, residual or activation")
+        op = ChainOp()
+        op.type, op.exchange = OP_GEMM, 1
+        op.A, op.lda, op.W, op.ldw = a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0)
+        op.N, op.K = w.shape[0], w.shape[1]
+        op.out_dtype = dtype_code(a.dtype)
+        op._keep = (a, w)
+        return op
     if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1] or a.stride(1) != 1 or w.stride(1) != 1:
         raise RuntimeError("chain gemm: a [M,K] and w [N,K] with contiguous rows required")
     if residual is not None and (residual.stride(-1) != 1 or residual.dtype != a.dtype):
@@ -48,6 +62,7 @@ def gemm_op(a, w, out, bias=None, residual=None, act=None, out_rows_per_batch=0,
     op.act = ACT_CODES[act] if not isinstance(act, int) else act
     op.c_rows_per_batch, op.c_batch_stride = out_rows_per_batch, out_batch_stride
     op.c_row_offset_device = _p(out_row_offset_device)
+    op.c_row_offset_limit = int(out_row_limit)
     op._keep = (a, w, out, bias, residual, out_row_offset_device)
     return op
 
@@ -65,6 +80,26 @@ def layernorm_op(x, y, gamma, beta, eps):
     return op
 
 
+def reduce_layernorm_op(sum_out, n_cols, bias=None, residual=None, y=None, gamma=None, beta=None, eps=1e-5):
+    """sum_out = (sum over ranks of the preceding exchanged product) + bias + residual, then
+    y = LayerNorm(sum_out; gamma, beta) (skipped when gamma is None).  sum_out / residual / y are
+    [M, n_cols] row-major."""
+    require_cuda(sum_out, bias, residual, y, gamma, beta)
+    if sum_out.dim() != 2 or sum_out.stride(1) != 1 or sum_out.shape[1] != n_cols:
+        raise RuntimeError("chain reduce: sum_out must be [M, n_cols] with contiguous rows")
+    if gamma is not None and (y is None or beta is None or not y.is_contiguous()):
+        raise RuntimeError("chain reduce: gamma needs beta and a contiguous y")
+    op = ChainOp()
+    op.type = OP_REDUCE_LAYERNORM
+    op.C, op.ldc = sum_out.data_ptr(), sum_out.stride(0)
+    op.bias, op.residual = _p(bias), _p(residual)
+    op.ldr = residual.stride(0) if residual is not None else 0
+    op.y, op.gamma, op.beta = _p(y), _p(gamma), _p(beta)
+    op.n2, op.eps = int(n_cols), float(eps)
+    op._keep = (sum_out, bias, residual, y, gamma, beta)
+    return op
+
+
 class Chain:
     """A fixed sequence of operations over fixed buffers, launched with run().  Needs a
     zero-filled workspace (arrival counters, stream-K partial sums): its own, or one passed in."""
@@ -75,12 +110,13 @@ class Chain:
         with torch.cuda.device(device):
             return lib().eb_decode_chain_workspace_bytes(ctypes.cast(arr, ctypes.c_void_p), len(ops), int(M))
 
-    def __init__(self, ops, M, dtype, device, workspace=None):
+    def __init__(self, ops, M, dtype, device, workspace=None, comm=None):
         if not 1 <= len(ops) <= MAX_OPS:
             raise RuntimeError(f"chain: 1..{MAX_OPS} operations")
         self.ops = (ChainOp * len(ops))(*ops)
         self._keep = [o._keep for o in ops]
         self.n, self.M, self.dtype = len(ops), int(M), dtype_code(dtype)
+        self.comm = comm                 # PeerExchange of the tensor-parallel group, for exchanged products
         with torch.cuda.device(device):
             nbytes = lib().eb_decode_chain_workspace_bytes(ctypes.cast(self.ops, ctypes.c_void_p), self.n, self.M)
         if nbytes == 0:
@@ -93,4 +129,5 @@ class Chain:
 
     def run(self):
         check(lib().eb_decode_chain(ctypes.cast(self.ops, ctypes.c_void_p), self.n, self.M, self.dtype, self.ws.data_ptr(),
-                                    self.ws.numel(), stream_ptr()), "decode_chain")
+                                    self.ws.numel(), self.comm.handle if self.comm is not None else None, stream_ptr()),
+              "decode_chain")

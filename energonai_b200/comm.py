@@ -1,49 +1,113 @@
-"""Peer-addressable exchange areas for the fused row-parallel GEMM + all-reduce.
+"""The tensor-parallel exchange context of the library (eb_comm_*) for one rank of a
+torch.distributed group.
 
-One `PeerExchange` per tensor-parallel group and process: a receive area and a flag area
-allocated as symmetric memory (every rank allocates the same sizes, the handles are exchanged
-through the process group, and each rank maps its peers' areas over NVLink).  torch's
-symmetric-memory allocator is used only for that plumbing; the data movement is done by the
-GEMM kernel's own peer stores (eb_gemm_allreduce).
+The library owns the context: it allocates this rank's receive area, exports a handle, maps the
+peers' areas (CUDA IPC over NVLink) and keeps the sequence number of the exchanges in device
+memory.  This module only carries the handles between the processes (one all_gather on the
+caller's process group) and holds the opaque pointer.  The data movement is done by the
+library's own kernels: the fused row-parallel GEMM + all-reduce (eb_gemm_allreduce), the
+generation-step chain (eb_decode_chain) and the stand-alone one-shot all-reduce (eb_allreduce).
 
 The reference reaches the same result with a blocking NCCL all-reduce inside colossalai's
-Linear1D_Row (used at energonai/model/attention.py:37, energonai/model/mlp.py:22).
+Linear1D_Row (used at energonai/model/attention.py:37, energonai/model/mlp.py:22), on process
+groups created by colossalai.launch (energonai/worker.py:27-28).
 """
 import ctypes
 
 import torch
 import torch.distributed as dist
 
-FLAG_SLOTS = 1024          # tiles of 128 output columns per (parity, source): N up to 131072
-
 
 class PeerExchange:
-    def __init__(self, group, rank, world, max_rows, max_cols):
-        import torch.distributed._symmetric_memory as symm_mem
-        from ._lib import lib
-        self.rank, self.world = rank, world
+    """One eb_comm.  `max_rows` x `max_cols` (16-bit elements) is the largest partial product one
+    exchange carries; rows are rounded up the way the generation-step GEMM pads its batch."""
+
+    def __init__(self, group, rank, world, max_rows, max_cols, wait_budget_s=None):
+        from ._lib import lib, check
+        self.rank, self.world, self.group = rank, world, group
         self.max_rows, self.max_cols = max_rows, max_cols
-        self.recv_bytes = lib().eb_gemm_allreduce_recv_bytes(world, max_rows, max_cols)
-        dev = torch.device("cuda", torch.cuda.current_device())
-        self.recv = symm_mem.empty(max(self.recv_bytes // 4, 4), dtype=torch.float32, device=dev)
-        self.flags = symm_mem.empty(2 * world * FLAG_SLOTS, dtype=torch.int32, device=dev)
-        self.recv.zero_()
-        self.flags.zero_()
-        self._h_recv = symm_mem.rendezvous(self.recv, group)
-        self._h_flags = symm_mem.rendezvous(self.flags, group)
-        PtrArray = ctypes.c_void_p * world
-        self.recv_ptrs = PtrArray(*[int(p) for p in self._h_recv.buffer_ptrs])
-        self.flag_ptrs = PtrArray(*[int(p) for p in self._h_flags.buffer_ptrs])
-        self.calls = 0
-        torch.cuda.synchronize()
-        dist.barrier(group=group)          # nobody sends before every area is zeroed and mapped
+        L = lib()
+        half = L.eb_comm_exchange_bytes(world, self._padded(max_rows), max_cols)
+        self.recv_bytes = 2 * ((half + 511) // 512 * 512)
+        handle = ctypes.c_void_p()
+        check(L.eb_comm_create(rank, world, self.recv_bytes, None, ctypes.byref(handle)), "comm_create", launches=0)
+        self.handle = handle
+        self._destroyed = False
+        if world > 1:
+            n = L.eb_comm_handle_bytes()
+            blob = (ctypes.c_ubyte * n)()
+            check(L.eb_comm_export_handle(self.handle, blob, n), "comm_export_handle", launches=0)
+            mine = torch.tensor(list(bytes(blob)), dtype=torch.uint8)
+            if dist.get_backend(group) == "nccl":
+                mine = mine.cuda()
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine, group=group)
+            blobs = bytes(torch.cat([p.cpu() for p in parts]).tolist())
+            if len(blobs) != world * n:
+                raise RuntimeError("comm: truncated handle exchange")
+            check(L.eb_comm_connect(self.handle, blobs, len(blobs)), "comm_connect", launches=0)
+            torch.cuda.synchronize()
+            dist.barrier(group=group)          # nobody sends before every area is zeroed and mapped
+        if wait_budget_s is not None:
+            self.set_wait_budget(wait_budget_s)
+
+    @classmethod
+    def from_pointers(cls, rank, world, recv_local, peer_ptrs, wait_budget_s=None):
+        """A context over receive areas the caller allocated and mapped itself (one process
+        driving several GPUs with peer access, or another symmetric allocator): `recv_local` is
+        this rank's area (a zero-filled CUDA uint8 tensor, kept alive by the object), `peer_ptrs`
+        the device addresses of all ranks' areas as seen from this process."""
+        from ._lib import lib, check
+        self = cls.__new__(cls)
+        self.rank, self.world, self.group = rank, world, None
+        self.max_rows = self.max_cols = None
+        self.recv_bytes = recv_local.numel()
+        self._area = recv_local
+        handle = ctypes.c_void_p()
+        check(lib().eb_comm_create(rank, world, self.recv_bytes, recv_local.data_ptr(), ctypes.byref(handle)), "comm_create",
+              launches=0)
+        self.handle, self._destroyed = handle, False
+        table = (ctypes.c_void_p * world)(*[int(p) for p in peer_ptrs])
+        check(lib().eb_comm_connect_pointers(self.handle, table), "comm_connect_pointers", launches=0)
+        if wait_budget_s is not None:
+            self.set_wait_budget(wait_budget_s)
+        return self
+
+    @staticmethod
+    def _padded(rows):
+        return 16 if rows <= 16 else 32 if rows <= 32 else 64 if rows <= 64 else 128
 
     def fits(self, rows, cols):
         from ._lib import lib
-        need = lib().eb_gemm_allreduce_recv_bytes(self.world, rows, cols)
-        return 0 < rows <= 128 and 0 < need <= self.recv_bytes and (cols + 127) // 128 <= FLAG_SLOTS
+        if not 0 < rows <= 128 or cols % 4:
+            return False
+        return lib().eb_comm_exchange_bytes(self.world, self._padded(rows), cols) <= self.recv_bytes // 2
 
-    def next_parity(self):
-        p = self.calls & 1
-        self.calls += 1
-        return p
+    def set_wait_budget(self, seconds):
+        from ._lib import lib, check
+        check(lib().eb_comm_set_wait_budget(self.handle, float(seconds)), "comm_set_wait_budget", launches=0)
+
+    def status(self, clear=True):
+        """(code, where, block, detail) of this context's own kernels (eb_allreduce)."""
+        from ._lib import lib, check
+        buf = (ctypes.c_int * 4)()
+        check(lib().eb_comm_status(self.handle, buf, 1 if clear else 0), "comm_status", launches=0)
+        return tuple(buf)
+
+    def all_reduce(self, t):
+        """In-place SUM of a contiguous CUDA tensor over the group with the library's one-shot
+        kernel (small messages; fp32 / fp16 / bf16)."""
+        from ._lib import lib, check, dtype_code, stream_ptr
+        if not t.is_cuda or not t.is_contiguous():
+            raise RuntimeError("comm.all_reduce: contiguous CUDA tensor required")
+        check(lib().eb_allreduce(self.handle, t.data_ptr(), t.numel(), dtype_code(t.dtype), stream_ptr()), "allreduce")
+        return t
+
+    def fits_bytes(self, nbytes):
+        return self.world * nbytes * 2 <= self.recv_bytes // 2 and nbytes % 8 == 0
+
+    def destroy(self):
+        if not self._destroyed:
+            from ._lib import lib
+            lib().eb_comm_destroy(self.handle)
+            self._destroyed = True

@@ -315,7 +315,8 @@ attention_decode_kernel(const AttnParams p) {
   griddep_launch();
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int Sk = p.kv_len_ptr ? *p.kv_len_ptr : p.Sk;
+  // a device-side length is clamped to the capacity the host stated (p.Sk, when positive)
+  const int Sk = p.kv_len_ptr ? max(1, p.Sk > 0 ? min(*p.kv_len_ptr, p.Sk) : *p.kv_len_ptr) : p.Sk;
   const int tiles_total = (Sk + kBN - 1) / kBN;
   const int tiles_per = (tiles_total + p.nsplit - 1) / p.nsplit;
   const int tile0 = split * tiles_per, tile1 = min(tiles_total, tile0 + tiles_per);

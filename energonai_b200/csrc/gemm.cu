@@ -33,7 +33,7 @@
 #include <cstdlib>
 #include <type_traits>
 
-#include "common.cuh"
+#include "comm.cuh"
 
 namespace eb {
 namespace {
@@ -49,18 +49,6 @@ constexpr uint32_t kBarrierBytes = 1024;      // head of shared memory: mbarrier
 
 __device__ int g_status[4];      // [0] code (0 = ok), [1] where, [2] block, [3] detail
 
-// Peer exchange of the fused row-parallel GEMM + all-reduce (generation orientation only).
-// Every rank owns a receive area [2 parities][world sources][tiles][128 rows][BN] in the operand
-// type (a thread's BN batch values are contiguous, so it moves them with 16-byte accesses) and a
-// flag area [2][world][tiles] u32, both in memory its peers can address over NVLink.
-struct CommParams {
-  int rank, world;               // world <= 1: no exchange
-  int parity;                    // alternates between consecutive calls (double buffering)
-  void *recv[8];                 // recv[r]: base of rank r's receive area (recv[rank] is local)
-  uint32_t *flags[8];            // flags[r]: base of rank r's flag area
-  int max_tiles;                 // flag slots per (parity, source)
-};
-
 struct GemmParams {
   int M, N, K;                   // logical problem: C[M,N] = A[M,K] W[N,K]^T
   int lane_rows, col_rows;       // rows of the lane-side / column-side operand (swap: N, M)
@@ -70,6 +58,7 @@ struct GemmParams {
   int c_rows_per_batch;          // 0: row m of C is at m*ldc; else (m / rpb)*c_batch_stride + (m % rpb)*ldc
   long long c_batch_stride;
   const int *c_row_offset_dev;   // optional device scalar: extra row offset of C (rows of ldc), read at run time
+  int c_row_limit;               // > 0: the device offset must lie in [0, limit); otherwise nothing is stored
   const void *bias;              // [N] or null
   const void *residual;          // [M, N] rows ldr apart, or null
   long long ldr;
@@ -81,7 +70,11 @@ struct GemmParams {
   int stages;                    // pipeline depth actually used (<= kMaxStages)
   int kpb;                       // k-blocks (64 columns each) per pipeline stage / barrier hand-over
   int static_w;                  // W may be read before the preceding kernel of the stream has finished
-  CommParams comm;
+  // Fused all-reduce of the generation orientation (comm.world > 1): the CTA that completes a
+  // tile sends this rank's partial product to every rank as flagged lines and adds up what the
+  // ranks sent it (see comm.cuh).  A thread's BN batch values of output column n are contiguous
+  // in the receive area: lines [source][n][BN / 4].
+  CommDev comm;
   // swap mode, optional: the A operand is the un-normalised input of a LayerNorm whose scale
   // was multiplied into W beforehand.  The kernel computes each row's mean / inverse std over
   // K itself and the last epilogue of a tile evaluates
@@ -191,20 +184,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ float ld_relaxed_sys_f32(const float *p) {
-  float v;
-  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-  return v;
-}
-
 // Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
 // 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups are 1024
 // bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
@@ -305,6 +284,16 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   return v;
 }
 
+// A run-time row offset outside [0, c_row_limit) would write past the caller's buffer (a cache
+// that was not sized for the step): nothing is stored and the status word says so.
+__device__ __forceinline__ bool row_in_limit(const GemmParams &p, int row) {
+  if (!p.c_row_offset_dev || p.c_row_limit <= 0 || (row >= 0 && row < p.c_row_limit)) return true;
+  if (atomicCAS(&g_status[0], 0, EB_ELIMIT) == 0) {
+    g_status[1] = 9; g_status[2] = blockIdx.x; g_status[3] = row;
+  }
+  return false;
+}
+
 __device__ __forceinline__ long long c_row_offset(const GemmParams &p, int m) {
   const long long extra = p.c_row_offset_dev ? (long long)__ldg(p.c_row_offset_dev) * p.ldc : 0;
   if (p.c_rows_per_batch <= 0) return (long long)m * p.ldc + extra;
@@ -333,7 +322,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
   const uint32_t tfull_bar = empty_bar + 8 * kMaxStages, tempty_bar = tfull_bar + 16;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kMaxStages + 5);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  volatile int *last_flag = reinterpret_cast<volatile int *>(tmem_slot + 2);   // two entries, alternating
   const uint32_t epi_bar = tempty_bar + 16;
   const uint32_t tiles_addr = smem_u32(smem) + kBarrierBytes;
 
@@ -353,7 +341,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
     }
     mbar_init(epi_bar, 128);               // rendezvous of the four epilogue warps
     *abort_flag = 0;
-    last_flag[0] = last_flag[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_lane) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_col) : "memory");
@@ -477,9 +464,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
     const int lrow = quarter * 32 + lane;           // lane-side row inside the tile
     const T *bias = reinterpret_cast<const T *>(p.bias);
     const T *res = reinterpret_cast<const T *>(p.residual);
+    // sequence number of this launch's exchange (the counter is advanced when the grid is done)
+    const uint32_t comm_seq = (SWAP && p.comm.world > 1) ? *reinterpret_cast<volatile unsigned int *>(p.comm.ctl + kCtlEpoch) + 1u : 0u;
     Scheduler<BN, SWAP> sched(p);
     Segment s;
-    int acc = 0, flag_slot = 0;
+    int acc = 0;
     uint32_t acc_phase = 0, epi_phase = 0;
     bool alive = true;
     // Rendezvous of the 128 epilogue threads with a bounded wait (a plain bar.sync could not
@@ -535,7 +524,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
       T r_early[kEarlyRes ? BN : 1];
       float b = 0.f, colsum = 0.f;
       // run-time row offset of C (the cache row of a generation step): one load, up front
-      const long long c_extra = (SWAP && p.c_row_offset_dev) ? (long long)__ldg(p.c_row_offset_dev) * p.ldc : 0;
+      const int c_row = (SWAP && p.c_row_offset_dev) ? __ldg(p.c_row_offset_dev) : 0;
+      const long long c_extra = (long long)c_row * p.ldc;
+      const bool row_ok = row_in_limit(p, c_row);
       if (SWAP) {
         const int n = s.lane_row0 + lrow;
         if (n < p.N) {
@@ -570,7 +561,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
         // tile's epilogue as long as its main loop), absent operands are zeros, and the
         // activation is chosen once per chunk: these warps are alone on their schedulers.
         const int m = s.lane_row0 + lrow;
-        const bool m_ok = m < p.M;
+        const bool m_ok = m < p.M && row_in_limit(p, p.c_row_offset_dev ? __ldg(p.c_row_offset_dev) : 0);
         const long long c_off = m_ok ? c_row_offset(p, m) : 0;
         const int n_base = s.col_tile * BN;
         const int act = p.act;
@@ -661,21 +652,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
 #pragma unroll
           for (int m = 0; m < BN; ++m)
             if (m < p.M) __stcg(mine + (size_t)m * kLanes + lrow, v[m]);
-          if (p.comm.world > 1) {
-            // the exchange below is a whole-CTA protocol: one arrival counter per tile
-            __threadfence();
-            if (!epi_sync()) { alive = false; continue; }
-            if (threadIdx.x == 64) {
-              const int arrived = atomicAdd(p.counters + 4 * s.lane_tile, 1);
-              const int is_last = arrived == last_cta - first_cta;
-              if (is_last) p.counters[4 * s.lane_tile] = 0;      // ready for the next call
-              last_flag[flag_slot] = is_last;
-            }
-            if (!epi_sync()) { alive = false; continue; }
-            do_epilogue = last_flag[flag_slot] != 0;         // the other slot is written next time
-            flag_slot ^= 1;
-            if (do_epilogue) __threadfence();
-          } else {
+          {
             // Each warp owns a quarter of the tile's rows in every CTA, so the hand-over is done
             // warp by warp (one counter per tile and quarter): no CTA-wide rendezvous, and the
             // release / acquire ride on the counter update itself.
@@ -747,19 +724,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
             }
           }
         }
-        if (do_epilogue && p.comm.world > 1) {
-          // Fused all-reduce: this CTA holds the rank's complete partial product of the tile.
-          // Push it into every rank's receive area (plain stores over NVLink), publish a flag
-          // per destination, wait (bounded) for the flags of all sources in the local area,
-          // then sum the sources in rank order, identically on every rank.
-          const CommParams &cm = p.comm;
-          const int tiles = (p.N + kLanes - 1) / kLanes;
-          const size_t slot = (size_t)tiles * kLanes * BN;                // elements per (parity, source)
-          const size_t row_off = ((size_t)s.lane_tile * kLanes + lrow) * BN;
-          const size_t my_off = ((size_t)cm.parity * cm.world + cm.rank) * slot + row_off;
+        if (do_epilogue && p.comm.world > 1 && n_ok) {
+          // Fused all-reduce: this thread holds the rank's complete partial products of output
+          // column n for every batch row.  They go to every rank (this one included) as flagged
+          // lines, rounded to the operand type (what an all-reduce of the product would carry);
+          // then the lines of all sources are collected from the local area and added in rank
+          // order, so every rank forms the bit-identical sum.  No fence and no rendezvous: a line
+          // is valid when it carries this exchange's sequence number.
+          const CommDev &cm = p.comm;
+          constexpr int kLines = BN / 4;
+          const unsigned long long per_src = (unsigned long long)p.N * kLines;            // lines per source
+          const unsigned long long half = (comm_seq & 1u) * cm.half_bytes;
           {
-            // partial sums travel in the operand type (as an NCCL all-reduce of the product would)
-            uint4 packed[BN / 8];
+            uint32_t packed[BN / 2];
 #pragma unroll
             for (int q = 0; q < BN / 8; ++q) {
               Vec16<T> pk;
@@ -767,62 +744,50 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
 #pragma unroll
               for (int j = 0; j < 8; ++j) tmp[j] = v[q * 8 + j];
               pk.pack(tmp);
-              packed[q] = pk.raw;
+              packed[q * 4 + 0] = pk.raw.x; packed[q * 4 + 1] = pk.raw.y;
+              packed[q * 4 + 2] = pk.raw.z; packed[q * 4 + 3] = pk.raw.w;
             }
+            const unsigned long long mine = half + ((unsigned long long)cm.rank * per_src + (unsigned long long)n * kLines) * 16ull;
             for (int r = 0; r < cm.world; ++r) {
-              uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<T *>(cm.recv[r]) + my_off);
 #pragma unroll
-              for (int q = 0; q < BN / 8; ++q) dst[q] = packed[q];
+              for (int q = 0; q < kLines; ++q) ll_store(cm.recv[r] + mine + q * 16, packed[2 * q], packed[2 * q + 1], comm_seq);
             }
           }
-          __threadfence_system();
-          if (!epi_sync()) { alive = false; continue; }
-          const int et = threadIdx.x - 64;                              // 0..127 among the epilogue threads
-          const size_t flag_idx = ((size_t)cm.parity * cm.world) * cm.max_tiles + s.lane_tile;
-          if (et < cm.world) st_release_sys(cm.flags[et] + flag_idx + (size_t)cm.rank * cm.max_tiles, 1u);
-          if (et < cm.world) {
-            uint32_t *mine = cm.flags[cm.rank] + flag_idx + (size_t)et * cm.max_tiles;
-            const unsigned long long t0 = globaltimer();
-            bool got = false;
-            for (unsigned it = 1; !got; ++it) {
-              got = ld_acquire_sys(mine) != 0u;
-              if (!got && (it & 63u) == 0) {
-                if (*abort_flag) break;
-                if (globaltimer() - t0 > kWaitBudgetNs) {
+#pragma unroll
+          for (int m = 0; m < BN; ++m) v[m] = 0.f;
+          bool lost = false;
+          for (int r = 0; r < cm.world && !lost; ++r) {
+            const unsigned char *src = cm.recv[cm.rank] + half + ((unsigned long long)r * per_src + (unsigned long long)n * kLines) * 16ull;
+            uint32_t d[BN / 2];
+            uint32_t pending = kLines >= 32 ? 0xffffffffu : (1u << (kLines & 31)) - 1u;
+            unsigned long long t0 = 0;
+            for (unsigned it = 0; pending; ++it) {
+#pragma unroll
+              for (int q = 0; q < kLines; ++q)
+                if ((pending >> q) & 1u)
+                  if (ll_load(src + q * 16, comm_seq, d[2 * q], d[2 * q + 1])) pending &= ~(1u << q);
+              if (pending && (it & 63u) == 63u) {
+                if (t0 == 0) t0 = globaltimer();
+                if (*abort_flag || globaltimer() - t0 > cm.wait_budget_ns) {
                   *abort_flag = 1;
                   if (atomicCAS(&g_status[0], 0, EB_ETIMEDOUT) == 0) {
-                    g_status[1] = 6; g_status[2] = blockIdx.x; g_status[3] = et;
+                    g_status[1] = 6; g_status[2] = blockIdx.x; g_status[3] = r;
                   }
+                  lost = true;
                   break;
                 }
               }
             }
-            if (got) *mine = 0u;                                        // consumed: ready for the next use of this slot
-          }
-          if (!epi_sync()) { alive = false; continue; }
-          if (*abort_flag) { alive = false; continue; }
-          {
-            const T *src = reinterpret_cast<const T *>(cm.recv[cm.rank]) + (size_t)cm.parity * cm.world * slot + row_off;
 #pragma unroll
-            for (int m = 0; m < BN; ++m) v[m] = 0.f;
-            for (int r = 0; r < cm.world; ++r) {
-              const uint4 *sp = reinterpret_cast<const uint4 *>(src + (size_t)r * slot);
-#pragma unroll
-              for (int q = 0; q < BN / 8; ++q) {
-                Vec16<T> pk;
-                asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(pk.raw.x), "=r"(pk.raw.y), "=r"(pk.raw.z), "=r"(pk.raw.w)
-                             : "l"(sp + q)
-                             : "memory");
-                float tmp[8];
-                pk.unpack(tmp);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[q * 8 + j] += tmp[j];
-              }
+            for (int q = 0; q < BN / 2; ++q) {
+              const float2 f = unpack2<T>(d[q]);
+              v[2 * q] += f.x;
+              v[2 * q + 1] += f.y;
             }
           }
+          if (lost) { alive = false; continue; }
         }
-        if (do_epilogue && n_ok) {
+        if (do_epilogue && n_ok && row_ok) {
           // offset of row m of C, advanced row by row (a division per row by the run-time
           // rows-per-batch cost 0.1 us each: 2 us per tile)
           long long row_off = c_extra + n;
@@ -900,6 +865,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
   // ---------------- teardown ----------------
   tcgen05_fence_before();
   __syncthreads();
+  if (SWAP && p.comm.world > 1 && threadIdx.x == 0) {
+    // the last CTA of the grid advances the exchange's sequence number for the next launch
+    unsigned int *ctl = p.comm.ctl;
+    const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(ctl + kCtlEpoch) + 1u;
+    __threadfence();
+    if (atomicAdd(ctl + kCtlBlocks, 1u) == gridDim.x - 1) {
+      ctl[kCtlBlocks] = 0u;
+      ctl[kCtlEpoch] = seq;
+      __threadfence();
+    }
+  }
   if (*abort_flag) {
     // bounded grace period for copies that may still be in flight to this CTA's shared memory
     const unsigned long long t0 = globaltimer();
@@ -966,17 +942,17 @@ int launch(const CUtensorMap &tl, const CUtensorMap &tc, const GemmParams &p, in
 inline int swap_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
 
 // Stream-K split of the swapped orientation: grid and units (pipeline stages of a tile) per CTA.
+// A short K (few stages per tile, the row-parallel GEMMs of a wide tensor-parallel group) is not
+// worth cutting: one CTA streams a whole tile in a few microseconds, which is less than the
+// partial-sum hand-over of a shared tile costs.
+constexpr long long kNoSplitStages = 10;
+
 inline void swap_split(int N, int K, int kpb, int *grid, int *units) {
   const long long tiles = (N + kLanes - 1) / kLanes, kblocks = (K + kBlockK - 1) / kBlockK;
   const long long nsk = (kblocks + kpb - 1) / kpb;
   const long long total = tiles * nsk;
   long long g = sm_count();
-  // A short K (few stages per tile, the row-parallel GEMMs of a wide tensor-parallel group) is
-  // not worth cutting: one CTA streams a whole tile in a few microseconds, which is less than
-  // the partial-sum hand-over of a shared tile costs.
-  static const int nosplit_env = getenv("EB_NOSPLIT_NSK") ? atoi(getenv("EB_NOSPLIT_NSK")) : -1;
-  const long long nosplit_nsk = nosplit_env >= 0 ? nosplit_env : 10;
-  if (nsk <= nosplit_nsk && tiles <= g) {
+  if (nsk <= kNoSplitStages && tiles <= g) {
     *units = (int)nsk;
     *grid = (int)tiles;
     return;
@@ -1030,7 +1006,7 @@ extern "C" size_t eb_decode_chain_workspace_bytes(const eb_chain_op *ops, int n_
 }
 
 extern "C" int eb_decode_chain(const eb_chain_op *ops, int n_ops, int M, int dtype, void *workspace,
-                               size_t workspace_bytes, void *stream) {
+                               size_t workspace_bytes, eb_comm *comm, void *stream) {
   EB_REQUIRE(ops && n_ops >= 1 && n_ops <= kMaxOps, "decode_chain: 1..%d operations", kMaxOps);
   EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "decode_chain: fp16 or bf16 only");
   EB_REQUIRE(M >= 1 && M <= kLanes, "decode_chain: M must be in [1, 128] (got %d)", M);
@@ -1043,35 +1019,29 @@ extern "C" int eb_decode_chain(const eb_chain_op *ops, int n_ops, int M, int dty
   ChainParams p{};
   ChainMaps maps;
   p.n_ops = n_ops; p.M = M;
-  static const int prefetch_env = getenv("EB_CHAIN_PREFETCH") ? atoi(getenv("EB_CHAIN_PREFETCH")) : -1;
-  p.prefetch = prefetch_env >= 0 ? (prefetch_env > 64 ? 64 : prefetch_env) : 8;
+  p.prefetch = 8;
   p.kpb = bn <= 32 ? 2 : 1;
+  // shared memory: [1 KB barriers][ring of stages][staging area of the exchange: 4 warps x BN rows x 32 values]
   const size_t stage_bytes = ((size_t)kLanes * 128 + (size_t)bn * 128) * p.kpb;
-  int stages = (int)((200 * 1024 - kBarrierBytes - 1024) / stage_bytes);
+  const size_t xpose_bytes = (size_t)bn * 256;
+  int stages = (int)((200 * 1024 - kBarrierBytes - 1024 - xpose_bytes) / stage_bytes);
   p.stages = stages > kMaxStages ? kMaxStages : (stages < 2 ? 2 : stages);
-  const size_t smem = kBarrierBytes + 1024 + (size_t)p.stages * stage_bytes;
+  p.xpose_off = (uint32_t)(p.stages * stage_bytes);
+  const size_t smem = kBarrierBytes + 1024 + (size_t)p.stages * stage_bytes + xpose_bytes;
   p.done = reinterpret_cast<int *>(workspace);
-  // diagnostics: with EB_CHAIN_TRACE=1 and a workspace with room behind the required part, every
-  // CTA leaves globaltimer stamps per operation there
-  static const bool trace_env = getenv("EB_CHAIN_TRACE") && atoi(getenv("EB_CHAIN_TRACE")) > 0;
-  const size_t trace_bytes = (size_t)grid * kMaxOps * 8 * sizeof(unsigned long long);
-  if (trace_env && workspace_bytes >= ((need + 255) / 256) * 256 + trace_bytes)
-    p.trace = reinterpret_cast<unsigned long long *>(reinterpret_cast<char *>(workspace) + ((need + 255) / 256) * 256);
   char *cursor = reinterpret_cast<char *>(workspace) + kChainPartialOffset;
   int rc;
   bool any_gemm = false;
+  int pending_exchange = -1;            // index of the exchange a kReduceLn must follow
   for (int i = 0; i < n_ops; ++i) {
     const eb_chain_op &o = ops[i];
     if (o.type == EB_OP_GEMM) {
       any_gemm = true;
-      EB_REQUIRE(o.A && o.W && o.C, "decode_chain: op %d: null GEMM operand", i);
-      EB_REQUIRE(o.N > 0 && o.K >= 8 && o.K % 8 == 0 && o.N % 8 == 0, "decode_chain: op %d: K and N must be multiples of 8", i);
-      EB_REQUIRE(o.lda >= o.K && o.ldw >= o.K && o.lda % 8 == 0 && o.ldw % 8 == 0 && o.ldc >= o.N,
-                 "decode_chain: op %d: bad leading dimensions", i);
-      EB_REQUIRE(!o.residual || (o.ldr >= o.N && o.ldr % 8 == 0), "decode_chain: op %d: bad residual stride", i);
-      EB_REQUIRE(o.out_dtype == dtype || o.out_dtype == EB_F32, "decode_chain: op %d: bad output type", i);
-      EB_REQUIRE(o.act >= EB_ACT_NONE && o.act <= EB_ACT_GELU_ERF, "decode_chain: op %d: unknown activation", i);
-      EB_REQUIRE(aligned16(o.A) && aligned16(o.W) && aligned16(o.C), "decode_chain: op %d: pointers must be 16-byte aligned", i);
+      EB_REQUIRE(pending_exchange < 0, "decode_chain: op %d: the exchange of op %d must be followed by EB_OP_REDUCE_LAYERNORM", i, i - 1);
+      EB_REQUIRE(o.A && o.W, "decode_chain: op %d: null GEMM operand", i);
+      EB_REQUIRE(o.N > 0 && o.K >= 8 && o.K % 8 == 0, "decode_chain: op %d: K must be a positive multiple of 8", i);
+      EB_REQUIRE(o.lda >= o.K && o.ldw >= o.K && o.lda % 8 == 0 && o.ldw % 8 == 0, "decode_chain: op %d: bad leading dimensions", i);
+      EB_REQUIRE(aligned16(o.A) && aligned16(o.W), "decode_chain: op %d: pointers must be 16-byte aligned", i);
       ChainGemm &g = p.g[i];
       p.type[i] = kOpGemm;
       g.N = o.N; g.K = o.K;
@@ -1080,9 +1050,25 @@ extern "C" int eb_decode_chain(const eb_chain_op *ops, int n_ops, int M, int dty
       g.tiles = (o.N + kLanes - 1) / kLanes;
       const long long total = (long long)g.tiles * g.nsk;
       EB_REQUIRE(total < (1ll << 30), "decode_chain: op %d too large", i);
-      g.units_per_cta = (int)((total + grid - 1) / grid);
+      g.units_per_cta = (g.nsk <= kNoSplitStages && g.tiles <= grid) ? g.nsk : (int)((total + grid - 1) / grid);
+      g.exchange = -1;
+      if (o.exchange) {
+        EB_REQUIRE(comm, "decode_chain: op %d exchanges its product: a context is needed", i);
+        EB_REQUIRE(!o.bias && !o.residual && o.act == EB_ACT_NONE, "decode_chain: op %d: bias, residual and activation belong to the reduction that follows an exchange", i);
+        EB_REQUIRE(o.N % 8 == 0, "decode_chain: op %d: an exchanged product needs N to be a multiple of 8", i);
+        EB_REQUIRE(comm_exchange_bytes(comm->world, M, o.N) <= comm->recv_bytes / 2,
+                   "decode_chain: op %d: %d x %d from %d ranks does not fit half of the receive area (%zu bytes)", i, M, o.N,
+                   comm->world, comm->recv_bytes / 2);
+        g.exchange = p.n_exchanges++;
+        pending_exchange = g.exchange;
+      } else {
+        EB_REQUIRE(o.C && aligned16(o.C) && o.ldc >= o.N, "decode_chain: op %d: bad output", i);
+        EB_REQUIRE(!o.residual || (o.ldr >= o.N && o.ldr % 8 == 0), "decode_chain: op %d: bad residual stride", i);
+        EB_REQUIRE(o.out_dtype == dtype || o.out_dtype == EB_F32, "decode_chain: op %d: bad output type", i);
+        EB_REQUIRE(o.act >= EB_ACT_NONE && o.act <= EB_ACT_GELU_ERF, "decode_chain: op %d: unknown activation", i);
+      }
       g.C = o.C; g.ldc = o.ldc; g.c_rows_per_batch = o.c_rows_per_batch; g.c_batch_stride = o.c_batch_stride;
-      g.c_row_offset_dev = o.c_row_offset_device;
+      g.c_row_offset_dev = o.c_row_offset_device; g.c_row_limit = o.c_row_offset_limit;
       g.bias = o.bias; g.residual = o.residual; g.ldr = o.ldr; g.act = o.act; g.out_f32 = o.out_dtype == EB_F32;
       EB_REQUIRE((size_t)g.tiles * sizeof(int) <= kChainTileCounterBytes, "decode_chain: op %d: N too large", i);
       g.counters = reinterpret_cast<int *>(reinterpret_cast<char *>(workspace) + kChainHeadBytes + i * kChainTileCounterBytes);
@@ -1091,16 +1077,41 @@ extern "C" int eb_decode_chain(const eb_chain_op *ops, int n_ops, int M, int dty
       if ((rc = make_map(&maps.w[i], o.W, dtype, o.N, o.K, o.ldw, kLanes))) return rc;
       if ((rc = make_map(&maps.x[i], o.A, dtype, M, o.K, o.lda, bn))) return rc;
     } else if (o.type == EB_OP_LAYERNORM) {
+      EB_REQUIRE(pending_exchange < 0, "decode_chain: op %d: the exchange of op %d must be followed by EB_OP_REDUCE_LAYERNORM", i, i - 1);
       EB_REQUIRE(o.x && o.y && o.gamma && o.beta && o.n2 > 0 && o.n2 % 8 == 0, "decode_chain: op %d: bad LayerNorm operands", i);
       EB_REQUIRE(aligned16(o.x) && aligned16(o.y) && aligned16(o.gamma) && aligned16(o.beta),
                  "decode_chain: op %d: pointers must be 16-byte aligned", i);
       p.type[i] = kOpLayerNorm;
-      p.l[i] = ChainLn{o.x, o.gamma, o.beta, o.y, o.n2, (float)o.eps};
+      ChainLn &l = p.l[i];
+      l = ChainLn{};
+      l.x = o.x; l.gamma = o.gamma; l.beta = o.beta; l.y = o.y; l.n2 = o.n2; l.eps = (float)o.eps;
+    } else if (o.type == EB_OP_REDUCE_LAYERNORM) {
+      EB_REQUIRE(pending_exchange >= 0 && i > 0 && ops[i - 1].type == EB_OP_GEMM && ops[i - 1].N == o.n2,
+                 "decode_chain: op %d: a reduction follows the exchanged GEMM whose N equals its n2", i);
+      EB_REQUIRE(o.C && aligned16(o.C) && o.ldc >= o.n2 && o.ldc % 8 == 0, "decode_chain: op %d: bad sum output", i);
+      EB_REQUIRE(!o.residual || (aligned16(o.residual) && o.ldr >= o.n2 && o.ldr % 8 == 0), "decode_chain: op %d: bad residual", i);
+      EB_REQUIRE(aligned16(o.bias), "decode_chain: op %d: misaligned bias", i);
+      EB_REQUIRE(!o.gamma || (o.beta && o.y && aligned16(o.y) && aligned16(o.gamma) && aligned16(o.beta)),
+                 "decode_chain: op %d: bad LayerNorm operands", i);
+      p.type[i] = kOpReduceLn;
+      ChainLn &l = p.l[i];
+      l = ChainLn{};
+      l.gamma = o.gamma; l.beta = o.beta; l.y = o.y; l.n2 = o.n2; l.eps = (float)o.eps;
+      l.bias = o.bias; l.residual = o.residual; l.ldr = o.ldr; l.sum_out = o.C; l.ld_sum = o.ldc;
+      l.exchange = pending_exchange;
+      pending_exchange = -1;
     } else {
       return fail(EB_EINVAL, "decode_chain: op %d: unknown type %d", i, o.type);
     }
   }
+  EB_REQUIRE(pending_exchange < 0, "decode_chain: the last operation exchanges its product but nothing reduces it");
   EB_REQUIRE(any_gemm, "decode_chain: a chain needs at least one GEMM");
+  if (p.n_exchanges > 0) {
+    int dev = -1;
+    cudaGetDevice(&dev);
+    EB_REQUIRE(comm->connected && comm->device == dev, "decode_chain: the context is not connected or belongs to another device");
+    p.comm = comm_dev(comm);
+  }
   cudaStream_t st = as_stream(stream);
 #define EB_CHAIN(BN) (dtype == EB_F16 ? launch_chain<__half, BN>(maps, p, grid, smem, st) \
                                       : launch_chain<__nv_bfloat16, BN>(maps, p, grid, smem, st))
@@ -1135,8 +1146,8 @@ extern "C" int eb_device_status(int *out4, int clear) {
 static int gemm_impl(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
                      const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
                      int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
-                     const int32_t *c_row_offset_device, int flags, void *workspace, size_t workspace_bytes,
-                     void *stream, const CommParams *comm, const float *ln_colsum = nullptr,
+                     const int32_t *c_row_offset_device, int c_row_offset_limit, int flags, void *workspace,
+                     size_t workspace_bytes, void *stream, const eb_comm *comm, const float *ln_colsum = nullptr,
                      const float *ln_bias = nullptr, double ln_eps = 0.0) {
   EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "gemm: operands must be fp16 or bf16 (got dtype %d)", dtype);
   if (ln_colsum || ln_bias) {
@@ -1152,10 +1163,13 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
   EB_REQUIRE((flags & ~EB_GEMM_STATIC_W) == 0, "gemm: unknown flag bits 0x%x", flags);
   if (M == 0 || N == 0) return EB_OK;
   EB_REQUIRE(A && W && C, "gemm: null operand");
-  EB_REQUIRE(K >= 8 && K % 8 == 0 && N % 8 == 0, "gemm: K and N must be positive multiples of 8 (K=%d N=%d)", K, N);
+  // the generation orientation (M <= 128) writes C one element at a time: any N will do there
+  EB_REQUIRE(K >= 8 && K % 8 == 0 && (N % 8 == 0 || M <= kLanes), "gemm: K, and N for M > 128, must be positive multiples of 8 (K=%d N=%d)", K, N);
   EB_REQUIRE(lda >= K && ldw >= K && lda % 8 == 0 && ldw % 8 == 0, "gemm: lda/ldw must be multiples of 8 and >= K");
-  EB_REQUIRE(ldc >= N && ldc % 8 == 0 && (!residual || (ldr >= N && ldr % 8 == 0)), "gemm: ldc/ldr must be multiples of 8 and >= N");
-  EB_REQUIRE(c_rows_per_batch >= 0 && (c_rows_per_batch == 0 || c_batch_stride % 8 == 0), "gemm: bad batch mapping of C");
+  EB_REQUIRE(ldc >= N && (ldc % 8 == 0 || M <= kLanes) && (!residual || (ldr >= N && (ldr % 8 == 0 || M <= kLanes))),
+             "gemm: ldc/ldr must be >= N (and multiples of 8 for M > 128)");
+  EB_REQUIRE(c_rows_per_batch >= 0 && (c_rows_per_batch == 0 || c_batch_stride % 8 == 0 || M <= kLanes), "gemm: bad batch mapping of C");
+  EB_REQUIRE(c_row_offset_limit >= 0, "gemm: negative row-offset limit");
   EB_REQUIRE(aligned16(A) && aligned16(W) && aligned16(C) && aligned16(bias) && aligned16(residual),
              "gemm: pointers must be 16-byte aligned");
   cudaStream_t st = as_stream(stream);
@@ -1164,13 +1178,20 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
   p.M = M; p.N = N; p.K = K;
   p.kblocks = (K + kBlockK - 1) / kBlockK;
   p.C = C; p.ldc = ldc; p.c_rows_per_batch = c_rows_per_batch; p.c_batch_stride = c_batch_stride;
-  p.c_row_offset_dev = c_row_offset_device;
+  p.c_row_offset_dev = c_row_offset_device; p.c_row_limit = c_row_offset_limit;
   p.static_w = (flags & EB_GEMM_STATIC_W) ? 1 : 0;
-  if (comm) p.comm = *comm;
   p.ln_colsum = ln_colsum; p.ln_bias = ln_bias; p.ln_x = A; p.ln_ldx = lda; p.ln_eps = (float)ln_eps;
-  EB_REQUIRE(!comm || comm->world <= 1 || M <= kLanes, "gemm_allreduce: the fused exchange serves M <= 128 only (M=%d)", M);
-  EB_REQUIRE(!comm || comm->world <= 1 || (long long)((N + kLanes - 1) / kLanes) <= comm->max_tiles,
-             "gemm_allreduce: N=%d needs more flag slots than the exchange area has", N);
+  if (comm && comm->world > 1) {
+    int dev = -1;
+    cudaGetDevice(&dev);
+    EB_REQUIRE(comm->connected && comm->device == dev, "gemm_allreduce: the context is not connected or belongs to another device");
+    EB_REQUIRE(M <= kLanes, "gemm_allreduce: the fused exchange serves M <= 128 only (M=%d)", M);
+    EB_REQUIRE(N % 4 == 0, "gemm_allreduce: N must be a multiple of 4");
+    EB_REQUIRE(comm_exchange_bytes(comm->world, swap_bn(M), N) <= comm->recv_bytes / 2,
+               "gemm_allreduce: %d x %d from %d ranks does not fit half of the receive area (%zu bytes)", swap_bn(M), N,
+               comm->world, comm->recv_bytes / 2);
+    p.comm = comm_dev(comm);
+  }
   p.bias = bias; p.residual = residual; p.ldr = ldr; p.act = act; p.out_f32 = out_dtype == EB_F32 && dtype != EB_F32;
 
   CUtensorMap tl, tc;
@@ -1181,11 +1202,9 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
     int grid;
     // k-blocks per stage: stages of about 36 KB keep the hand-over count per byte low
     const size_t sub_bytes = (size_t)kLanes * 128 + (size_t)bn * 128;
-    static const int kpb_env = getenv("EB_KPB") ? atoi(getenv("EB_KPB")) : 0;
-    p.kpb = kpb_env > 0 ? (kpb_env > 8 ? 8 : kpb_env) : (bn <= 32 ? 2 : 1);
+    p.kpb = bn <= 32 ? 2 : 1;
     const size_t stage_bytes = sub_bytes * p.kpb;
-    static const int budget_env = getenv("EB_SMEM_KB") ? atoi(getenv("EB_SMEM_KB")) : 0;
-    const size_t budget = (size_t)(budget_env > 0 ? budget_env : 200) * 1024;
+    const size_t budget = (size_t)200 * 1024;
     const size_t fixed = kBarrierBytes + 1024;                      // barriers, alignment
     int stages = (int)((budget - fixed) / stage_bytes);
     stages = stages > kMaxStages ? kMaxStages : (stages < 2 ? 2 : stages);
@@ -1235,50 +1254,31 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
 extern "C" int eb_gemm(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
                        const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
                        int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
-                       const int32_t *c_row_offset_device, int flags, void *workspace, size_t workspace_bytes,
-                       void *stream) {
+                       const int32_t *c_row_offset_device, int c_row_offset_limit, int flags, void *workspace,
+                       size_t workspace_bytes, void *stream) {
   return gemm_impl(A, lda, W, ldw, C, ldc, bias, residual, ldr, M, N, K, dtype, out_dtype, act, c_rows_per_batch,
-                   c_batch_stride, c_row_offset_device, flags, workspace, workspace_bytes, stream, nullptr);
+                   c_batch_stride, c_row_offset_device, c_row_offset_limit, flags, workspace, workspace_bytes, stream,
+                   nullptr);
 }
 
 extern "C" int eb_gemm_ln(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
                           const float *ln_colsum, const float *ln_bias, double eps, const void *residual,
                           long long ldr, int M, int N, int K, int dtype, int out_dtype, int act,
                           int c_rows_per_batch, long long c_batch_stride, const int32_t *c_row_offset_device,
-                          int flags, void *workspace, size_t workspace_bytes, void *stream) {
+                          int c_row_offset_limit, int flags, void *workspace, size_t workspace_bytes, void *stream) {
   EB_REQUIRE(ln_colsum && ln_bias, "gemm_ln: ln_colsum and ln_bias are required");
   return gemm_impl(A, lda, W, ldw, C, ldc, nullptr, residual, ldr, M, N, K, dtype, out_dtype, act, c_rows_per_batch,
-                   c_batch_stride, c_row_offset_device, flags, workspace, workspace_bytes, stream, nullptr, ln_colsum,
-                   ln_bias, eps);
-}
-
-extern "C" size_t eb_gemm_allreduce_recv_bytes(int world, int M, int N) {
-  if (M <= 0 || M > kLanes || N <= 0 || world <= 0) return 0;
-  const size_t tiles = (N + kLanes - 1) / kLanes;
-  return (size_t)2 * world * tiles * kLanes * swap_bn(M) * 2;     // 16-bit elements
+                   c_batch_stride, c_row_offset_device, c_row_offset_limit, flags, workspace, workspace_bytes, stream,
+                   nullptr, ln_colsum, ln_bias, eps);
 }
 
 extern "C" int eb_gemm_allreduce(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
                                  const void *bias, const void *residual, long long ldr, int M, int N, int K,
                                  int dtype, int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
-                                 const int32_t *c_row_offset_device, int flags, void *workspace,
-                                 size_t workspace_bytes, int rank, int world, void *const *peer_recv,
-                                 void *const *peer_flags, size_t recv_bytes, int flag_slots_per_source, int parity,
-                                 void *stream) {
-  EB_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world, "gemm_allreduce: bad rank %d / world %d", rank, world);
-  EB_REQUIRE(parity == 0 || parity == 1, "gemm_allreduce: parity must be 0 or 1");
-  CommParams cm{};
-  cm.rank = rank; cm.world = world; cm.parity = parity; cm.max_tiles = flag_slots_per_source;
-  if (world > 1) {
-    EB_REQUIRE(peer_recv && peer_flags && flag_slots_per_source > 0, "gemm_allreduce: missing exchange areas");
-    EB_REQUIRE(recv_bytes >= eb_gemm_allreduce_recv_bytes(world, M, N),
-               "gemm_allreduce: receive areas of %zu bytes are too small for world %d, M %d, N %d", recv_bytes, world, M, N);
-    for (int r = 0; r < world; ++r) {
-      EB_REQUIRE(peer_recv[r] && peer_flags[r], "gemm_allreduce: null exchange area for rank %d", r);
-      cm.recv[r] = peer_recv[r];
-      cm.flags[r] = reinterpret_cast<uint32_t *>(peer_flags[r]);
-    }
-  }
+                                 const int32_t *c_row_offset_device, int c_row_offset_limit, int flags,
+                                 void *workspace, size_t workspace_bytes, eb_comm *comm, void *stream) {
+  EB_REQUIRE(comm, "gemm_allreduce: null context");
   return gemm_impl(A, lda, W, ldw, C, ldc, bias, residual, ldr, M, N, K, dtype, out_dtype, act, c_rows_per_batch,
-                   c_batch_stride, c_row_offset_device, flags, workspace, workspace_bytes, stream, &cm);
+                   c_batch_stride, c_row_offset_device, c_row_offset_limit, flags, workspace, workspace_bytes, stream,
+                   comm);
 }

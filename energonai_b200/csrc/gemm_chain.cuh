@@ -15,7 +15,7 @@
 #pragma once
 
 constexpr int kMaxOps = 8;
-constexpr int kOpGemm = 0, kOpLayerNorm = 1;
+constexpr int kOpGemm = 0, kOpLayerNorm = 1, kOpReduceLn = 2;
 
 struct ChainGemm {
   int N, K, kblocks, nsk;        // nsk = pipeline stages per 128-row tile
@@ -26,11 +26,17 @@ struct ChainGemm {
   int c_rows_per_batch;
   long long c_batch_stride;
   const int *c_row_offset_dev;
+  int c_row_limit;               // > 0: the device row offset must lie in [0, limit)
   const void *bias, *residual;
   long long ldr;
   int act, out_f32;
   float *partial;                // [grid][2][BN][128]
   int *counters;                 // [tiles], zero between launches
+  // exchange >= 0: a row-parallel product of a tensor-parallel group.  Instead of being stored,
+  // the finished tiles go to every rank's receive area as flagged lines [source][m][N / 4]
+  // (comm.cuh), with sequence number epoch + 1 + exchange; the kReduceLn operation that follows
+  // adds the ranks' contributions up.  -1: an ordinary GEMM.
+  int exchange;
 };
 
 struct ChainLn {
@@ -38,6 +44,14 @@ struct ChainLn {
   void *y;
   int n2;
   float eps;
+  // kOpReduceLn only: x_sum = sum over ranks of the preceding exchange + bias + residual is
+  // written to `sum_out` (rounded to the operand type) and normalised into y (gamma == null: no
+  // normalisation, y unused).
+  const void *bias, *residual;
+  long long ldr;
+  void *sum_out;
+  long long ld_sum;
+  int exchange;
 };
 
 struct ChainParams {
@@ -47,7 +61,9 @@ struct ChainParams {
   ChainGemm g[kMaxOps];
   ChainLn l[kMaxOps];
   int *done;                     // [kMaxOps] arrival counters, zero between launches
-  unsigned long long *trace;     // optional [grid][kMaxOps][8] globaltimer stamps (diagnostics), or null
+  CommDev comm;                  // exchange context (world >= 1) when n_exchanges > 0
+  int n_exchanges;               // exchanges this launch performs; the epoch advances by that much
+  uint32_t xpose_off;            // shared-memory offset (from the tiles) of the push staging area
 };
 
 struct ChainMaps {
@@ -99,10 +115,6 @@ __device__ __noinline__ bool chain_wait_done(const int *done, int op, int count,
   }
 }
 
-#define EB_TRACE(op, slot)                                                                         \
-  do {                                                                                             \
-    if (p.trace) p.trace[((size_t)blockIdx.x * kMaxOps + (op)) * 8 + (slot)] = globaltimer();      \
-  } while (0)
 
 template <typename T, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -130,7 +142,6 @@ chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ Cha
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    EB_TRACE(0, 7);
     for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
@@ -217,7 +228,6 @@ chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ Cha
               bool ok = x_op == 0 ? true : x_op - 1 <= ready_upto;
               if (!ok && ld_acquire_gpu(p.done + x_op - 1) >= grid) {
                 ready_upto = x_op - 1; ok = true; act |= 8;
-                EB_TRACE(x_op, 1);
               }
               if (ok) act |= 2;
             }
@@ -228,7 +238,6 @@ chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ Cha
           const ChainGemm &g = p.g[w_op];
           const int tile = wc.tile, sk = wc.sk;
           const uint32_t fb = full_bar + 8 * w_slot;
-          if (lane == 0 && wc.pos == (int)blockIdx.x * g.units_per_cta) EB_TRACE(w_op, 0);
           const int nvalid = g.kblocks - sk * kpb < kpb ? g.kblocks - sk * kpb : kpb;
           if (lane == 0) mbar_expect_tx(fb, (uint32_t)nvalid * sub_bytes);
           __syncwarp(movers_mask);
@@ -308,7 +317,6 @@ chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ Cha
           for (int sk = sk0; sk < sk1; ++sk) {
             if (!mbar_wait(full_bar + 8 * slot, phase, abort_flag, 3)) { ok = false; break; }
             tcgen05_fence_after();
-            if (c.pos == (int)blockIdx.x * g.units_per_cta && sk == sk0) EB_TRACE(op, 5);
             for (int j = 0; j < kpb && sk * kpb + j < g.kblocks; ++j) {
               const uint32_t a_addr = tiles_addr + slot * stage_bytes + j * sub_bytes;
               const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + lane_bytes);
@@ -324,7 +332,6 @@ chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ Cha
           if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
           c.pos += sk1 - sk0;
         }
-        EB_TRACE(op, 6);
       }
     }
   } else {

@@ -20,12 +20,15 @@ def workspace(device, nbytes):
 
 
 def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out_rows_per_batch=0,
-         out_batch_stride=0, out_ld=None, out_row_offset_device=None, static_weight=False, peer=None, ln_fold=None):
+         out_batch_stride=0, out_ld=None, out_row_offset_device=None, out_row_limit=0, static_weight=False, peer=None,
+         ln_fold=None):
     """a [M,K] (row stride allowed), w [N,K]; returns out [M,N].
 
     `out`, if given, receives the result; with out_rows_per_batch > 0 row m is written at
     element (m // rpb) * out_batch_stride + (m % rpb) * out_ld of `out` (a view into a cache);
-    out_row_offset_device (int32 device scalar) adds that many rows of out_ld at run time.
+    out_row_offset_device (int32 device scalar) adds that many rows of out_ld at run time;
+    out_row_limit > 0 is the number of rows that offset may address (beyond it the kernel
+    stores nothing and raises the device status word).
     static_weight=True promises that `w` is not being written by earlier work still in flight
     on the stream (model weights), which lets the kernel prefetch it early.
     ln_fold=(colsum, bias32, eps), from fold_layernorm(): `a` is the un-normalised input of a
@@ -60,7 +63,7 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
         check(lib().eb_gemm_ln(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out_ld, ptr(colsum), ptr(bias32), float(eps),
                                ptr(residual), residual.stride(0) if residual is not None else 0, M, N, K,
                                dtype_code(a.dtype), dtype_code(out_dtype), code, out_rows_per_batch, out_batch_stride,
-                               ptr(out_row_offset_device), 1 if static_weight else 0, ptr(ws),
+                               ptr(out_row_offset_device), int(out_row_limit), 1 if static_weight else 0, ptr(ws),
                                ws.numel() if ws is not None else 0, stream_ptr()), "gemm_ln")
         return out
     if peer is not None and peer.world > 1:
@@ -69,15 +72,14 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
         check(lib().eb_gemm_allreduce(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out_ld, ptr(bias), ptr(residual),
                                       residual.stride(0) if residual is not None else 0, M, N, K, dtype_code(a.dtype),
                                       dtype_code(out_dtype), code, out_rows_per_batch, out_batch_stride,
-                                      ptr(out_row_offset_device), 1 if static_weight else 0, ptr(ws),
-                                      ws.numel() if ws is not None else 0, peer.rank, peer.world, peer.recv_ptrs,
-                                      peer.flag_ptrs, peer.recv_bytes, 1024, peer.next_parity(), stream_ptr()),
+                                      ptr(out_row_offset_device), int(out_row_limit), 1 if static_weight else 0, ptr(ws),
+                                      ws.numel() if ws is not None else 0, peer.handle, stream_ptr()),
               "gemm_allreduce")
         return out
     check(lib().eb_gemm(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out_ld, ptr(bias), ptr(residual),
                         residual.stride(0) if residual is not None else 0, M, N, K, dtype_code(a.dtype),
                         dtype_code(out_dtype), code, out_rows_per_batch, out_batch_stride,
-                        ptr(out_row_offset_device), 1 if static_weight else 0, ptr(ws),
+                        ptr(out_row_offset_device), int(out_row_limit), 1 if static_weight else 0, ptr(ws),
                         ws.numel() if ws is not None else 0, stream_ptr()), "gemm")
     return out
 
@@ -105,5 +107,5 @@ def device_status(clear=True):
     """(code, where, block, detail) of the current device's bounded-wait status word."""
     import ctypes
     buf = (ctypes.c_int * 4)()
-    check(lib().eb_device_status(ctypes.cast(buf, ctypes.c_void_p), 1 if clear else 0), "device_status")
+    check(lib().eb_device_status(ctypes.cast(buf, ctypes.c_void_p), 1 if clear else 0), "device_status", launches=0)
     return tuple(buf)

@@ -157,7 +157,7 @@ class MultiHeadAttention1D(nn.Module):
                 if buf.shape[0] != B:
                     raise RuntimeError("attention: the cache was sized for another batch")
                 gemm(x, w, bias=b, static_weight=True, out=buf, out_rows_per_batch=1, out_batch_stride=buf.stride(0), out_ld=buf.stride(1),
-                     out_row_offset_device=kv_state[0:1], ln_fold=fold)
+                     out_row_offset_device=kv_state[0:1], out_row_limit=cap, ln_fold=fold)
                 ctx = attention_decode(buf[:, :, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, cap, mask=mask,
                                        scale=self.scaling, q_in_cache=True, kv_len_device=kv_state[1:2])
             ctx = ctx.view(B, 1, hl)

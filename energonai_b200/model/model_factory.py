@@ -50,6 +50,7 @@ class PipelineModel(nn.Module):
         self.disable_past_cache = disable_past_cache
         self.eos_token_id = 50256          # the reference hard-codes this stop id (model_factory.py:133)
         self.use_cuda_graph = True         # greedy generation steps are captured once and replayed
+        self.stop_check_every = 16         # replayed steps between two host reads of the stop condition
         # optional: generation steps run each layer as two launches (attention + one chained
         # kernel for the six GEMM / LayerNorm operations around it).  Off by default: measured on
         # OPT-13B, batch 16, the chained step is about 6 % slower than one kernel per operation
@@ -78,52 +79,84 @@ class PipelineModel(nn.Module):
 
     # One generation step with every position-dependent quantity read from device memory, so
     # that the same sequence of launches can be captured once and replayed.
-    def _chain_ok(self, batch_size, model_dtype):
+    def _chain_mode(self, batch_size, model_dtype):
+        """How the generation step is launched: None = one kernel per operation; "local" = per
+        layer one attention kernel and one chained kernel for the six GEMM / LayerNorm operations
+        around it (single rank, opt-in); "exchange" = the same chain on a tensor-parallel group,
+        with the two all-reduces of a layer carried inside it (the default there: with the weight
+        shards of a wide group every separate launch is mostly fixed cost, and the wait for the
+        other ranks hides under the next operation's weight stream)."""
         from ..tp import get_tp
+        tp = get_tp()
         blk = self.blocks[0] if len(self.blocks) else None
-        return (self.use_decode_chain and blk is not None and get_tp().world_size == 1 and batch_size <= 128
-                and model_dtype in (torch.float16, torch.bfloat16) and not blk.apply_post_layernorm
-                and not self.disable_past_cache and self.first and self.last)
+        ok = (blk is not None and batch_size <= 128 and model_dtype in (torch.float16, torch.bfloat16)
+              and not blk.apply_post_layernorm and not self.disable_past_cache and self.first and self.last)
+        if not ok:
+            return None
+        if tp.world_size > 1:
+            fits = tp.peer is not None and tp.peer.fits(batch_size, self.hidden_size)
+            return "exchange" if fits and os.environ.get("EB_CHAIN", "1") != "0" else None
+        return "local" if self.use_decode_chain else None
 
     def _build_chains(self, st):
         """The generation step as 1 + depth chained launches over fixed buffers:
         [norm1_0, qkv_0], then per layer, after its attention kernel,
         [out-proj + residual, norm2, FC1 + activation, FC2 + residual, norm1 / qkv of the next
         layer (or the final norm and the LM head)]  (energonai/model/endecoder.py:48-70,
-        model_factory.py:124-131)."""
-        from ..chain import Chain, gemm_op, layernorm_op
+        model_factory.py:124-131).  On a tensor-parallel group the two row-parallel products are
+        exchanged and "+ bias + residual, LayerNorm" becomes the reduction that follows them."""
+        from ..chain import Chain, gemm_op, layernorm_op, reduce_layernorm_op
+        from ..tp import get_tp
         B = st["tok"].shape[0]
         dev, dt = st["tok"].device, st["add_mask"].dtype
         h = self.hidden_size
         f = self.blocks[0].mlp.dense_1.out_per_rank
+        exchange = st["chain_mode"] == "exchange"
+        comm = get_tp().peer if exchange else None
         new = lambda *shape, dtype=dt: torch.empty(shape, dtype=dtype, device=dev)
         xa, xb, x1, n, a = new(B, h), new(B, h), new(B, h), new(B, h), new(B, f)
         ctx = new(B, self.blocks[0].attn.local_hidden)
         logits = new(B, self.head.weight.shape[0], dtype=torch.float32)
 
-        def head_ops(i, x):      # norm1 + QKV of layer i, or the model's final norm + LM head
+        def norm_of(i):          # the LayerNorm in front of layer i's attention, or the model's final norm
+            return self.norm if i == len(self.blocks) else self.blocks[i].norm1
+
+        def proj_op(i):          # QKV of layer i into its cache row, or the LM head
             if i == len(self.blocks):
-                return [layernorm_op(x, n, self.norm.module.weight, self.norm.module.bias, self.norm.eps),
-                        gemm_op(n, self.head.weight, logits, bias=self.head.dense.bias)]
+                return gemm_op(n, self.head.weight, logits, bias=self.head.dense.bias)
             blk = self.blocks[i]
             w, b = blk.attn._packed()
             buf = blk.attn.past_cache.buf
-            return [layernorm_op(x, n, blk.norm1.module.weight, blk.norm1.module.bias, blk.norm1.eps),
-                    gemm_op(n, w, buf, bias=b, out_rows_per_batch=1, out_batch_stride=buf.stride(0), out_ld=buf.stride(1),
-                            out_row_offset_device=st["kv_state"][0:1])]
+            return gemm_op(n, w, buf, bias=b, out_rows_per_batch=1, out_batch_stride=buf.stride(0), out_ld=buf.stride(1),
+                           out_row_offset_device=st["kv_state"][0:1], out_row_limit=buf.shape[1])
 
-        groups = [head_ops(0, xa)]
+        def ln_op(x, norm):
+            return layernorm_op(x, n, norm.module.weight, norm.module.bias, norm.eps)
+
+        groups = [[ln_op(xa, norm_of(0)), proj_op(0)]]
         x_in, x_out = xa, xb
         for i, blk in enumerate(self.blocks):
-            ops = [gemm_op(ctx, blk.attn.dense.weight, x1, bias=blk.attn.dense.bias, residual=x_in),
-                   layernorm_op(x1, n, blk.norm2.module.weight, blk.norm2.module.bias, blk.norm2.eps),
-                   gemm_op(n, blk.mlp.dense_1.weight, a, bias=blk.mlp.dense_1.bias, act=blk.mlp.act_code),
-                   gemm_op(a, blk.mlp.dense_2.weight, x_out, bias=blk.mlp.dense_2.bias, residual=x1)]
-            groups.append(ops + head_ops(i + 1, x_out))
+            nxt = norm_of(i + 1)
+            if exchange:
+                ops = [gemm_op(ctx, blk.attn.dense.weight, exchange=True),
+                       reduce_layernorm_op(x1, h, bias=blk.attn.dense.bias, residual=x_in, y=n, gamma=blk.norm2.module.weight,
+                                           beta=blk.norm2.module.bias, eps=blk.norm2.eps),
+                       gemm_op(n, blk.mlp.dense_1.weight, a, bias=blk.mlp.dense_1.bias, act=blk.mlp.act_code),
+                       gemm_op(a, blk.mlp.dense_2.weight, exchange=True),
+                       reduce_layernorm_op(x_out, h, bias=blk.mlp.dense_2.bias, residual=x1, y=n, gamma=nxt.module.weight,
+                                           beta=nxt.module.bias, eps=nxt.eps),
+                       proj_op(i + 1)]
+            else:
+                ops = [gemm_op(ctx, blk.attn.dense.weight, x1, bias=blk.attn.dense.bias, residual=x_in),
+                       ln_op(x1, blk.norm2),
+                       gemm_op(n, blk.mlp.dense_1.weight, a, bias=blk.mlp.dense_1.bias, act=blk.mlp.act_code),
+                       gemm_op(a, blk.mlp.dense_2.weight, x_out, bias=blk.mlp.dense_2.bias, residual=x1),
+                       ln_op(x_out, nxt), proj_op(i + 1)]
+            groups.append(ops)
             x_in, x_out = x_out, x_in
         nbytes = max(Chain.workspace_bytes(g, B, dev) for g in groups)
         ws = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
-        st["chains"] = [Chain(g, B, dt, dev, workspace=ws) for g in groups]
+        st["chains"] = [Chain(g, B, dt, dev, workspace=ws, comm=comm) for g in groups]
         st["chain_bufs"] = {"x0": xa, "ctx": ctx, "logits": logits}
 
     def _chain_step(self, st):
@@ -141,10 +174,14 @@ class PipelineModel(nn.Module):
                              mask=st["add_mask"], scale=at.scaling, q_in_cache=True, kv_len_device=st["kv_state"][1:2],
                              out=bufs["ctx"])
             chains[i + 1].run()
-        return bufs["logits"]
+        logits = bufs["logits"]
+        if self.head.vocab_parallel:
+            from ..tp import get_tp
+            logits = get_tp().all_gather_last_dim(logits)
+        return logits
 
     def _static_step(self, st):
-        if st.get("use_chain"):
+        if st.get("chain_mode"):
             tok = self._chain_step(st).argmax(-1)
             st["out_ids"].index_copy_(1, st["kv_state"][1:2].to(torch.long), tok.view(-1, 1))
             st["tok"].copy_(tok)
@@ -179,7 +216,7 @@ class PipelineModel(nn.Module):
                   "out_ids": torch.empty((batch_size, tgt_len), dtype=ids_dtype, device=dev),
                   "tok": torch.empty((batch_size,), dtype=ids_dtype, device=dev),
                   "kv_state": torch.zeros(2, dtype=torch.int32, device=dev),
-                  "use_chain": self._chain_ok(batch_size, model_dtype)}
+                  "chain_mode": self._chain_mode(batch_size, model_dtype)}
             self._decode_state = st
         return st
 
@@ -242,6 +279,7 @@ class PipelineModel(nn.Module):
         st["kv_state"].copy_(torch.tensor([cur_len, cur_len + 1], dtype=torch.int32), non_blocking=False)
         use_graph = greedy and self.use_cuda_graph and (record is None or record.get("allow_graph", False))
         produced = cur_len + 1
+        checked = cur_len + 1                                  # columns of out_ids already tested for the stop condition
         for pos in range(cur_len + 1, tgt_len):
             if use_graph:
                 if st["graph"] is None and pos == cur_len + 1:
@@ -260,18 +298,30 @@ class PipelineModel(nn.Module):
                 else:
                     st["graph"].replay()
                     replayed += st["launches"]
-                tok = st["tok"]
-            else:
-                hidden_states = self.embed(tok.view(-1, 1), past_key_values_length=pos - 1)
-                mask4 = st["add_mask"][:, :pos].view(batch_size, 1, 1, pos)
-                for block in self.blocks:
-                    hidden_states = block(hidden_states=hidden_states, attention_mask=mask4, first_cache=False)
-                logits = self._last_logits(hidden_states, record)
-                if record is not None:
-                    record.setdefault("logits", []).append(logits.clone())
-                tok = logits.argmax(-1) if greedy else self.generate(out_ids[:, :pos], logits, top_k=top_k, top_p=top_p,
-                                                                     temperature=temperature)
-                out_ids[:, pos] = tok
+                mark()
+                # The reference stops when every sequence has just produced the stop token
+                # (model_factory.py:133-134).  Asking after every step would make the host wait for
+                # the device once per token; replays are queued ahead instead and the question is
+                # asked for a window of steps at a time.  Steps queued beyond the stopping point
+                # only wrote cache rows and columns that are cut off below.
+                if (pos - cur_len) % self.stop_check_every == 0 or pos == tgt_len - 1:
+                    hit = (out_ids[:, checked:pos + 1] == self.eos_token_id).all(0).nonzero()
+                    if hit.numel():
+                        produced = checked + int(hit[0])
+                        break
+                    checked = pos + 1
+                produced = pos + 1
+                continue
+            hidden_states = self.embed(tok.view(-1, 1), past_key_values_length=pos - 1)
+            mask4 = st["add_mask"][:, :pos].view(batch_size, 1, 1, pos)
+            for block in self.blocks:
+                hidden_states = block(hidden_states=hidden_states, attention_mask=mask4, first_cache=False)
+            logits = self._last_logits(hidden_states, record)
+            if record is not None:
+                record.setdefault("logits", []).append(logits.clone())
+            tok = logits.argmax(-1) if greedy else self.generate(out_ids[:, :pos], logits, top_k=top_k, top_p=top_p,
+                                                                 temperature=temperature)
+            out_ids[:, pos] = tok
             mark()
             if torch.all(tok == self.eos_token_id):
                 break

@@ -138,6 +138,50 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
                       void *sum_out, const void *gamma, const void *beta, int64_t n1, int n2, double eps, int in_dtype,
                       int out_dtype, void *stream);
 
+/* ---- tensor-parallel exchange context --------------------------------------------------------
+ *
+ * One eb_comm per rank of a tensor-parallel group (one process per GPU).  It takes the place of
+ * what the reference obtains from colossalai.launch (energonai/worker.py:27-28: the NCCL
+ * process groups) and of its unbuilt NCCL-id helper
+ * (energonai/kernel/cuda_native/csrc/get_ncclid.cpp:104-127), for the exchanges this library
+ * performs itself: the all-reduce of the row-parallel layers (colossalai's Linear1D_Row,
+ * constructed at energonai/model/attention.py:37 and energonai/model/mlp.py:22).
+ *
+ * Each rank owns a receive area its peers write into over NVLink with plain stores.  Set-up:
+ *   eb_comm_create(rank, world, recv_bytes, NULL, &c)        allocates and zeroes the local area
+ *   eb_comm_export_handle(c, blob, n)                        n = eb_comm_handle_bytes()
+ *   ... the caller gathers every rank's blob with its own process group, in rank order ...
+ *   eb_comm_connect(c, all_blobs, world * n)                 maps the peers' areas (CUDA IPC)
+ *   ... a barrier of the caller's: nobody exchanges before everybody is connected ...
+ * A caller that maps peer memory itself (one process driving several GPUs, or another symmetric
+ * allocator) passes its own area as recv_local and the peers' addresses to
+ * eb_comm_connect_pointers instead.  recv_bytes bounds what one exchange may carry:
+ * eb_comm_exchange_bytes(world, rows, cols) bytes per HALF of the area for a [rows, cols] 16-bit
+ * matrix (data travels with a sequence number beside every 4 bytes, so it takes twice its size).
+ * All ranks must issue the same exchanges in the same order.  A wait on a peer that lasts longer
+ * than the budget (1 s unless changed) is abandoned: the kernel records EB_ETIMEDOUT in the
+ * context (eb_comm_status) or in the device status word (eb_device_status), its result is then
+ * unspecified and the ranks' sequence numbers no longer agree: tear the group down.  One host
+ * thread at a time per context; exchanges sharing a context must not overlap on the device. */
+typedef struct eb_comm eb_comm;
+EB_API size_t eb_comm_handle_bytes(void);
+EB_API size_t eb_comm_exchange_bytes(int world, int rows, int cols);
+EB_API int eb_comm_create(int rank, int world, size_t recv_bytes, void *recv_local, eb_comm **out);
+EB_API int eb_comm_export_handle(const eb_comm *comm, void *blob, size_t blob_bytes);
+EB_API int eb_comm_connect(eb_comm *comm, const void *all_blobs, size_t all_blobs_bytes);
+EB_API int eb_comm_connect_pointers(eb_comm *comm, void *const *peer_recv);
+EB_API int eb_comm_set_wait_budget(eb_comm *comm, double seconds);
+EB_API int eb_comm_status(eb_comm *comm, int *out4, int clear);
+EB_API int eb_comm_destroy(eb_comm *comm);
+
+/* In-place SUM of buf[count] (dtype fp32 / fp16 / bf16, sums formed in fp32 in rank order, so
+ * every rank holds the bit-identical result) over the ranks of `comm`: each rank stores its
+ * buffer into every rank's receive area and adds up what it received ("one-shot": one NVLink
+ * crossing, meant for the kilobyte-to-megabyte messages of generation steps; NCCL remains the
+ * tool for prompt-sized tensors).  buf 8-byte aligned, count * size a multiple of 8 bytes,
+ * world * count * size * 2 <= recv_bytes / 2.  Replaces dist.all_reduce inside Linear1D_Row. */
+EB_API int eb_allreduce(eb_comm *comm, void *buf, size_t count, int dtype, void *stream);
+
 /* ---- dense layers (tcgen05 tensor-core GEMM) --------------------------------------------- */
 
 /* C = act(A . W^T + bias) + residual, fp32 accumulation in tensor memory.
@@ -153,9 +197,11 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
  *   projection write straight into a [batch, max_len, width] cache at a position offset).
  *   c_row_offset_device, if non-NULL, is a device int32 read by the kernel: that many further
  *   rows (of ldc elements) are added to every row's offset, so a captured launch can append
- *   at a position that advances between replays.
- *   K, N, all leading dimensions and c_batch_stride must be multiples of 8, pointers 16-byte
- *   aligned.
+ *   at a position that advances between replays.  c_row_offset_limit > 0 bounds it: a device
+ *   value outside [0, limit) stores nothing and records EB_ELIMIT in the device status word
+ *   (the caller's buffer was not sized for that position).
+ *   K must be a multiple of 8 and pointers 16-byte aligned; for M > 128 also N, all leading
+ *   dimensions and c_batch_stride (for M <= 128 the output is written element by element).
  * The kernel is launched so that it may begin before the preceding kernel of the stream has
  * finished; it reads A, bias and residual only after that kernel completed, and W too unless
  * flags has EB_GEMM_STATIC_W.
@@ -168,31 +214,26 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
  * workspace may be NULL for M > 128. */
 EB_API int eb_gemm(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc, const void *bias,
             const void *residual, long long ldr, int M, int N, int K, int dtype, int out_dtype, int act,
-            int c_rows_per_batch, long long c_batch_stride, const int32_t *c_row_offset_device, int flags,
-            void *workspace, size_t workspace_bytes, void *stream);
+            int c_rows_per_batch, long long c_batch_stride, const int32_t *c_row_offset_device,
+            int c_row_offset_limit, int flags, void *workspace, size_t workspace_bytes, void *stream);
 EB_API size_t eb_gemm_workspace_bytes(int M, int N, int K);
 
 /* Row-parallel GEMM with the tensor-parallel all-reduce fused into its epilogue, for the
  * generation orientation (M <= 128).  Replaces "F.linear, then dist.all_reduce, then + bias" of
  * colossalai's Linear1D_Row (the row-parallel layers constructed at
  * energonai/model/attention.py:37 and energonai/model/mlp.py:22).  Arguments as eb_gemm, plus the
- * exchange areas: every rank owns a receive area of eb_gemm_allreduce_recv_bytes(world, M, N)
- * bytes (or more) and a flag area of 2*world*flag_slots_per_source uint32 (zero before first
- * use), both addressable by its peers (NVLink peer mapping); peer_recv[r] / peer_flags[r] are
- * HOST arrays of `world` device pointers to rank r's areas as mapped in this process.  The CTA
- * that completes a tile stores its partial (rounded to the operand type, as an all-reduce of the
- * product would see it) into every rank's receive area with plain 16-byte peer stores, publishes one flag per destination, waits (bounded, 1 s, see eb_device_status) for all
- * sources' flags in its own area, and sums the sources in fp32 in rank order, so every rank obtains the
- * bit-identical result; bias, activation and residual are applied after the sum on every rank.
- * `parity` must alternate (0,1,0,1,...) over the successive calls that share the areas, in the
- * same order on all ranks.  world == 1 degenerates to eb_gemm. */
+ * exchange context.  The thread that completes the batch values of an output column stores them
+ * (rounded to the operand type, as an all-reduce of the product would see them) into every
+ * rank's receive area over NVLink, then adds up what all ranks sent it, in rank order, so every
+ * rank obtains the bit-identical result; bias, activation and residual are applied after the
+ * sum on every rank.  One launch = one exchange of the context (see eb_comm above):
+ * eb_comm_exchange_bytes(world, M rounded up to 16 / 32 / 64 / 128, N) must fit half of the
+ * receive area, N must be a multiple of 4.  A context of world 1 degenerates to eb_gemm. */
 EB_API int eb_gemm_allreduce(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
                       const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
                       int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
-                      const int32_t *c_row_offset_device, int flags, void *workspace, size_t workspace_bytes,
-                      int rank, int world, void *const *peer_recv, void *const *peer_flags, size_t recv_bytes,
-                      int flag_slots_per_source, int parity, void *stream);
-EB_API size_t eb_gemm_allreduce_recv_bytes(int world, int M, int N);
+                      const int32_t *c_row_offset_device, int c_row_offset_limit, int flags, void *workspace,
+                      size_t workspace_bytes, eb_comm *comm, void *stream);
 
 /* eb_gemm for M <= 32 rows with a LayerNorm folded in (generation steps): A holds the
  * UN-normalised rows x [M, K] and W the weights already multiplied by the LayerNorm scale,
@@ -207,17 +248,27 @@ EB_API size_t eb_gemm_allreduce_recv_bytes(int world, int M, int N);
 EB_API int eb_gemm_ln(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
                const float *ln_colsum, const float *ln_bias, double eps, const void *residual, long long ldr,
                int M, int N, int K, int dtype, int out_dtype, int act, int c_rows_per_batch,
-               long long c_batch_stride, const int32_t *c_row_offset_device, int flags, void *workspace,
-               size_t workspace_bytes, void *stream);
+               long long c_batch_stride, const int32_t *c_row_offset_device, int c_row_offset_limit, int flags,
+               void *workspace, size_t workspace_bytes, void *stream);
 
 /* ---- a chain of generation-step operations in one launch ----------------------------------- */
 
 #define EB_OP_GEMM 0
 #define EB_OP_LAYERNORM 1
+#define EB_OP_REDUCE_LAYERNORM 2
 
-/* One operation of eb_decode_chain.  GEMM: C = act(A . W^T + bias) + residual with the fields of
- * eb_gemm (A [M,K], W [N,K], static weights).  LayerNorm: y = gamma * norm(x) + beta over M rows
- * of n2 elements (x, y, gamma, beta in the chain's dtype). */
+/* One operation of eb_decode_chain.
+ * EB_OP_GEMM: C = act(A . W^T + bias) + residual with the fields of eb_gemm (A [M,K], W [N,K],
+ *   static weights).  With `exchange` != 0 the product is this rank's part of a row-parallel
+ *   layer: it is not stored but sent to every rank of the chain's context (bias, residual and
+ *   act must be unset, C is unused), and the next operation must be EB_OP_REDUCE_LAYERNORM.
+ * EB_OP_LAYERNORM: y = gamma * norm(x) + beta over M rows of n2 elements (x, y, gamma, beta in
+ *   the chain's dtype).
+ * EB_OP_REDUCE_LAYERNORM: t = (sum over ranks of the preceding exchanged product) + bias +
+ *   residual, rounded to the chain's dtype and written to C (rows ldc apart); then
+ *   y = gamma * norm(t) + beta (gamma NULL: no normalisation).  This is the all-reduce, bias and
+ *   skip connection of Linear1D_Row followed by the LayerNorm of the next sub-layer
+ *   (energonai/model/endecoder.py:56-63).  n2 = the product's N. */
 typedef struct eb_chain_op {
   int type;
   const void *A; long long lda; const void *W; long long ldw; void *C; long long ldc;
@@ -225,6 +276,8 @@ typedef struct eb_chain_op {
   int N, K, out_dtype, act, c_rows_per_batch;
   long long c_batch_stride;
   const int32_t *c_row_offset_device;
+  int c_row_offset_limit;
+  int exchange;
   const void *x; void *y; const void *gamma; const void *beta;
   int n2;
   double eps;
@@ -241,9 +294,13 @@ typedef struct eb_chain_op {
  * eb_decode_chain_workspace_bytes(...) bytes, 16-byte aligned, zero-filled once before first
  * use; launches sharing it must not overlap on the device.  All grid-wide waits are bounded
  * (1 s, eb_device_status).  The kernel needs every SM to host one of its CTAs at the same time:
- * do not run it concurrently with other work that pins shared memory on the device. */
+ * do not run it concurrently with other work that pins shared memory on the device.
+ * `comm` (NULL unless an operation exchanges): the tensor-parallel context; a launch performs
+ * as many exchanges of it as it has exchanged products, and while the grid waits for the other
+ * ranks' parts the weights of the following GEMM keep arriving, so the NVLink flight and the
+ * ranks' skew hide under the weight stream. */
 EB_API int eb_decode_chain(const eb_chain_op *ops, int n_ops, int M, int dtype, void *workspace,
-                    size_t workspace_bytes, void *stream);
+                    size_t workspace_bytes, eb_comm *comm, void *stream);
 EB_API size_t eb_decode_chain_workspace_bytes(const eb_chain_op *ops, int n_ops, int M);
 
 /* ---- fused attention ----------------------------------------------------------------------- */
@@ -270,7 +327,8 @@ EB_API int eb_attention_prefill(const void *q, const void *k, const void *v, voi
  * h*head_dim: q_row_stride 0 for a plain [batch, heads*head_dim] tensor, or the cache row
  * stride when the query projection sits in the cache row of the new token.  All kv_len cached
  * keys are visible.  kv_len_device, if non-NULL, is a device int32 that overrides
- * kv_len at run time (so a captured launch can be replayed while the cache grows).  The key
+ * kv_len at run time (so a captured launch can be replayed while the cache grows); kv_len, when
+ * positive, is then the capacity the device value is clamped to.  The key
  * range is split over `nsplit` CTAs per (sequence, head); for nsplit > 1 `scratch` must hold
  * eb_attention_decode_scratch_bytes(...) bytes, 16-byte aligned, zero-filled once before
  * first use.  Calls sharing a scratch must not overlap on the device. */

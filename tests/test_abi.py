@@ -71,11 +71,33 @@ def test_chain_op_struct_matches_the_header(tmp_path):
 def test_new_entry_points_validate_before_any_cuda_call():
     L = _lib.lib()
     # eb_gemm_ln: the folded vectors are required, and only generation-step batches are served
-    assert L.eb_gemm_ln(None, 8, None, 8, None, 8, None, None, 1e-5, None, 0, 4, 8, 8, _lib.F16, _lib.F16, 0, 0, 0, None, 0,
+    assert L.eb_gemm_ln(None, 8, None, 8, None, 8, None, None, 1e-5, None, 0, 4, 8, 8, _lib.F16, _lib.F16, 0, 0, 0, None, 0, 0,
                         None, 0, None) == -1
     assert "ln_colsum" in _lib.last_error()
-    assert L.eb_decode_chain(None, 0, 16, _lib.F16, None, 0, None) == -1
+    assert L.eb_decode_chain(None, 0, 16, _lib.F16, None, 0, None, None) == -1
     assert L.eb_decode_chain_workspace_bytes(None, 0, 16) == 0
+
+
+def test_exchange_context_validates_before_any_cuda_call():
+    """Wrong group sizes, undersized areas and null contexts are refused with a message; none of
+    these calls reaches the CUDA runtime."""
+    L = _lib.lib()
+    out = ctypes.c_void_p()
+    assert L.eb_comm_create(0, 0, 1 << 20, None, ctypes.byref(out)) == -1 and "world" in _lib.last_error()
+    assert L.eb_comm_create(3, 2, 1 << 20, None, ctypes.byref(out)) == -1 and "rank" in _lib.last_error()
+    assert L.eb_comm_create(0, 9, 1 << 20, None, ctypes.byref(out)) == -1
+    assert L.eb_comm_create(0, 2, 1000, None, ctypes.byref(out)) == -1 and "512" in _lib.last_error()
+    assert L.eb_comm_create(0, 2, 1 << 20, None, None) == -1
+    assert out.value is None
+    assert L.eb_comm_handle_bytes() == 64
+    assert L.eb_comm_exchange_bytes(8, 16, 5120) == 8 * 16 * 5120 * 4
+    assert L.eb_comm_exchange_bytes(0, 16, 5120) == 0
+    assert L.eb_allreduce(None, None, 8, _lib.F16, None) == -1 and "null context" in _lib.last_error()
+    assert L.eb_comm_status(None, None, 0) == -1
+    assert L.eb_comm_connect(None, None, 0) == -1
+    assert L.eb_comm_destroy(None) == 0
+    assert L.eb_gemm_allreduce(None, 8, None, 8, None, 8, None, None, 0, 4, 8, 8, _lib.F16, _lib.F16, 0, 0, 0, None, 0, 0, None,
+                               0, None, None) == -1
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -85,9 +85,10 @@ def test_two_gpu_block_matches_oracle(use_peer):
     assert all(ret.get(r) for r in range(world)), dict(ret)
 
 
-def _model_worker(rank, world, port, ret):
+def _model_worker(rank, world, port, ret, use_peer=False):
     """A small OPT-shaped PipelineModel with vocab-parallel embedding and LM head on `world` GPUs
-    against the same weights run on one rank."""
+    against the same weights run on one rank.  use_peer: the generation steps run as chained
+    launches that carry the all-reduces over NVLink peer memory (the library's own exchange)."""
     import torch.distributed as dist
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     torch.cuda.set_device(rank)
@@ -110,12 +111,33 @@ def _model_worker(rank, world, port, ret):
         mask[1, :4] = 0
         record = {}
         want = full(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1, record=record)
-        tp.init_tp(world)
+        ctx = tp.init_tp(world)
+        if use_peer:
+            ctx.enable_peer_exchange(16, 256)
+            # the stand-alone one-shot all-reduce against NCCL, several sizes and dtypes
+            for dt, n in ((torch.float16, 4096), (torch.bfloat16, 1024 * 40), (torch.float32, 20)):
+                t = (torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rank)) * 3).to(dt)
+                want_t = t.float().clone()
+                dist.all_reduce(want_t)
+                for _ in range(3):
+                    got_t = ctx.peer.all_reduce(t.clone())
+                assert float((got_t.float() - want_t).abs().max()) <= 2e-2 * float(want_t.abs().max()) + 1e-6
+                both = [torch.empty_like(got_t) for _ in range(world)]
+                dist.all_gather(both, got_t)
+                assert all(torch.equal(both[0], b) for b in both)      # bit-identical on every rank
+            assert ctx.peer.status()[0] == 0
         model = PipelineModel(vocab_parallel=True, **kw).cuda().eval()
         model.load_state_dict(shard_model_state(full.state_dict(), rank, world, vocab_parallel=True))
         assert model.embed.word_embeddings.weight.shape[0] == 1024 // world
         record_tp = {}
         got = model(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1, record=record_tp)
+        if use_peer:
+            from energonai_b200.gemm import device_status
+            replayed = model(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1)      # captured chain launches
+            assert model._decode_state["chain_mode"] == "exchange" and model._decode_state["graph"] is not None
+            assert float((replayed[:, 11:15] == want[:, 11:15]).float().mean()) >= 0.9
+            assert device_status()[0] == 0
+            got = replayed
         # prompt-pass logits: the same numbers up to the all-reduce's summation order
         a, b = record_tp["logits"][0].float(), record["logits"][0].float()
         ok = bool(((a - b).abs() <= 2e-2 * b.abs().max()).all())
@@ -131,9 +153,10 @@ def _model_worker(rank, world, port, ret):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_vocab_parallel_model():
+@pytest.mark.parametrize("use_peer", [False, True])
+def test_two_gpu_vocab_parallel_model(use_peer):
     import torch.multiprocessing as mp
     world, port = 2, _free_port()
     ret = mp.Manager().dict()
-    mp.spawn(_model_worker, args=(world, port, ret), nprocs=world, join=True)
+    mp.spawn(_model_worker, args=(world, port, ret, use_peer), nprocs=world, join=True)
     assert all(ret.get(r) for r in range(world)), dict(ret)
