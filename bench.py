@@ -261,8 +261,10 @@ def exposed_exchange(model, cfg, ids_d, mask_d, tgt, prefill_ms, step_ms):
     from energonai_b200.comm import PeerExchange
     ctx = tp.get_tp()
     real_peer, real_all_reduce, real_gather = ctx.peer, ctx.all_reduce, ctx.all_gather_last_dim
-    area = torch.zeros(real_peer.recv_bytes if real_peer is not None else 1 << 20, dtype=torch.uint8, device="cuda")
-    solo = PeerExchange.from_pointers(0, 1, area, [area.data_ptr()])
+    from energonai_b200._lib import lib
+    line_b, bulk_b = (real_peer.line_bytes, real_peer.bulk_bytes) if real_peer is not None else (1 << 20, 0)
+    area = torch.zeros(lib().eb_comm_area_bytes(line_b, bulk_b), dtype=torch.uint8, device="cuda")
+    solo = PeerExchange.from_pointers(0, 1, area, [area.data_ptr()], line_bytes=line_b)
     solo.max_rows, solo.max_cols = cfg["batch"], cfg["hidden"]
     saved_state = model._decode_state
     try:
@@ -384,8 +386,11 @@ def run_ours(args):
         if os.environ.get("EB_PEER", "1") != "0":
             # generation steps: the all-reduces run inside the library's own kernels over NVLink peer memory
             try:
-                ctx.enable_peer_exchange(128, cfg["hidden"])
-                exchange_kind = "prompt pass: NCCL all-reduce; generation steps: inside the chained kernel, NVLink peer stores"
+                bulk = cfg["batch"] * cfg["prompt"] if os.environ.get("EB_PEER_PROMPT", "1") != "0" else 0
+                ctx.enable_peer_exchange(128, cfg["hidden"], bulk_rows=bulk)
+                exchange_kind = ("prompt pass: " + ("reduce-scatter in the GEMM epilogue + reduce/broadcast kernel, NVLink peer stores"
+                                                    if bulk else "NCCL all-reduce") +
+                                 "; generation steps: inside the chained kernel, NVLink peer stores")
             except Exception as e:          # no peer mapping on this box: NCCL carries every all-reduce
                 ctx.peer = None
                 if rank == 0:

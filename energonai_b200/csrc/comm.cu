@@ -68,26 +68,37 @@ __global__ void __launch_bounds__(kArThreads) allreduce_kernel(const CommDev c, 
   }
   bool failed = false;
   for (unsigned long long i = first; i < lines; i += stride) {
+    // all sources' lines are requested together and looked at afterwards
+    LlLine got[8];
+    const unsigned char *base = c.recv[c.rank] + half + i * 16ull;
+    unsigned long long t0 = 0;
+    for (unsigned it = 0;; ++it) {
+      bool all = true;
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        if (s < c.world) got[s] = ll_fetch(base + (unsigned long long)s * lines * 16ull);
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        if (s < c.world) all = all && got[s].valid(seq);
+      if (all || failed) break;
+      if ((it & 63u) == 63u) {
+        if (t0 == 0) t0 = comm_timer();
+        else if (comm_timer() - t0 > c.wait_budget_ns) {
+          int missing = 0;
+#pragma unroll
+          for (int s = 7; s >= 0; --s)
+            if (s < c.world && !got[s].valid(seq)) missing = s;
+          comm_record_timeout(c, 20, missing);
+          failed = true;              // give up on this and every later line: the call has failed
+        }
+      }
+    }
     float acc[Payload<T>::N];
 #pragma unroll
     for (int e = 0; e < Payload<T>::N; ++e) acc[e] = 0.f;
-    for (int s = 0; s < c.world; ++s) {
-      const unsigned char *line = c.recv[c.rank] + half + ((unsigned long long)s * lines + i) * 16ull;
-      uint32_t d0 = 0, d1 = 0;
-      bool got = ll_load(line, seq, d0, d1);
-      if (!got && !failed) {
-        const unsigned long long t0 = comm_timer();
-        for (unsigned it = 1; !got; ++it) {
-          got = ll_load(line, seq, d0, d1);
-          if (!got && (it & 63u) == 0 && comm_timer() - t0 > c.wait_budget_ns) {
-            comm_record_timeout(c, 20, s);
-            failed = true;            // give up on this and every later line: the call has failed
-            break;
-          }
-        }
-      }
-      Payload<T>::add(acc, d0, d1);
-    }
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+      if (s < c.world) Payload<T>::add(acc, got[s].d0(), got[s].d1());
     data[i] = Payload<T>::pack(acc);
   }
   // the last block to finish advances the sequence number for the next exchange
@@ -125,12 +136,16 @@ extern "C" size_t eb_comm_exchange_bytes(int world, int rows, int cols) {
   return comm_exchange_bytes(world, rows, cols);
 }
 
-extern "C" int eb_comm_create(int rank, int world, size_t recv_bytes, void *recv_local, eb_comm **out) {
+extern "C" size_t eb_comm_area_bytes(size_t line_bytes, size_t bulk_bytes) { return kSignalBytes + line_bytes + bulk_bytes; }
+
+extern "C" int eb_comm_create(int rank, int world, size_t line_bytes, size_t bulk_bytes, void *recv_local, eb_comm **out) {
   EB_REQUIRE(out, "comm_create: null result pointer");
   *out = nullptr;
   EB_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world, "comm_create: bad rank %d / world %d", rank, world);
-  EB_REQUIRE(recv_bytes >= 4096 && recv_bytes % 512 == 0, "comm_create: the receive area must be a multiple of 512 bytes (>= 4096)");
+  EB_REQUIRE(line_bytes >= 4096 && line_bytes % 512 == 0, "comm_create: the flagged-line region must be a multiple of 512 bytes (>= 4096)");
+  EB_REQUIRE(bulk_bytes % 512 == 0, "comm_create: the bulk region must be a multiple of 512 bytes");
   EB_REQUIRE(!recv_local || (reinterpret_cast<uintptr_t>(recv_local) & 255u) == 0, "comm_create: recv_local must be 256-byte aligned");
+  const size_t recv_bytes = kSignalBytes + line_bytes + bulk_bytes;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) {
     cudaGetLastError();
@@ -139,6 +154,7 @@ extern "C" int eb_comm_create(int rank, int world, size_t recv_bytes, void *recv
   eb_comm *c = new (std::nothrow) eb_comm();
   if (!c) return fail(EB_ECUDA, "comm_create: out of host memory");
   c->rank = rank; c->world = world; c->device = dev; c->recv_bytes = recv_bytes;
+  c->line_bytes = line_bytes; c->bulk_bytes = bulk_bytes;
   c->wait_budget_ns = 1000ull * 1000ull * 1000ull;
   cudaError_t e = cudaSuccess;
   if (recv_local) {
@@ -258,6 +274,169 @@ extern "C" int eb_comm_destroy(eb_comm *c) {
   return EB_OK;
 }
 
+
+namespace eb {
+namespace {
+
+constexpr int kRbThreads = 256;
+
+// One lane per source: announces this rank at barrier `seq` (slot 0 or 1) to every rank.
+__device__ __forceinline__ void barrier_signal(const CommDev &c, int slot, uint32_t seq) {
+  if ((int)threadIdx.x < c.world)
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(c.sig[threadIdx.x] + slot * 8 + c.rank), "r"(seq) : "memory");
+}
+// One lane per source: waits (bounded) until every rank has announced itself.  True on success.
+__device__ __forceinline__ bool barrier_wait(const CommDev &c, int slot, uint32_t seq, int where) {
+  bool ok = true;
+  if ((int)threadIdx.x < c.world) {
+    const unsigned int *w = c.sig[c.rank] + slot * 8 + threadIdx.x;
+    unsigned long long t0 = 0;
+    for (unsigned it = 0;; ++it) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(w) : "memory");
+      if ((int)(v - seq) >= 0) break;
+      if ((it & 63u) == 63u) {
+        if (t0 == 0) t0 = comm_timer();
+        else if (comm_timer() - t0 > c.wait_budget_ns) {
+          comm_record_timeout(c, where, (int)threadIdx.x);
+          ok = false;
+          break;
+        }
+      }
+    }
+  }
+  return ok;
+}
+
+// The second kernel of the bulk all-reduce (comm.cuh): rows [rank * rpr, (rank + 1) * rpr) of
+// the [M, N] tensor are summed over the `world` staged partials (+ bias + residual), rounded to
+// T and stored into every rank's gather area.  16-byte pieces, one per thread and step; a
+// warp's stores cover 512 contiguous bytes of a row, locally and over NVLink.
+template <typename T>
+__global__ void __launch_bounds__(kRbThreads) reduce_broadcast_kernel(const CommDev c, long long M, int N, long long rpr,
+                                                                      unsigned long long stage_off, unsigned long long gather_off,
+                                                                      const T *bias, const T *residual, long long ldr) {
+  griddep_launch();
+  griddep_wait();
+  __shared__ int s_ok;
+  const uint32_t seq = *reinterpret_cast<volatile unsigned int *>(c.ctl + kCtlBarrier) + 1u;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  // everybody's partial products are in place once every rank's GEMM has completed
+  if (blockIdx.x == 0) {
+    __threadfence_system();
+    barrier_signal(c, 0, seq);
+  }
+  if (!barrier_wait(c, 0, seq, 21)) s_ok = 0;
+  __syncthreads();
+  const long long row0 = (long long)c.rank * rpr;
+  const long long my_rows = s_ok ? (M - row0 < rpr ? (M - row0 > 0 ? M - row0 : 0) : rpr) : 0;
+  const int packs = N / 8;
+  const long long total = my_rows * packs;
+  const T *stage = reinterpret_cast<const T *>(c.bulk[c.rank] + stage_off);
+  for (long long i = (long long)blockIdx.x * kRbThreads + threadIdx.x; i < total; i += (long long)gridDim.x * kRbThreads) {
+    const long long lr = i / packs;
+    const int n = (int)(i - lr * packs) * 8;
+    Vec16<T> part[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+      if (s < c.world) part[s].raw = __ldcg(reinterpret_cast<const uint4 *>(stage + ((long long)s * rpr + lr) * N + n));
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (s < c.world) {
+        float f[8];
+        part[s].unpack(f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += f[e];
+      }
+    }
+    if (bias) {
+      Vec16<T> b;
+      b.load(bias + n);
+      float f[8];
+      b.unpack(f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    if (residual) {
+      Vec16<T> r;
+      r.load(residual + (row0 + lr) * ldr + n);
+      float f[8];
+      r.unpack(f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    Vec16<T> o;
+    o.pack(acc);
+    const unsigned long long off = gather_off + (unsigned long long)((row0 + lr) * N + n) * sizeof(T);
+    for (int r = 0; r < c.world; ++r) *reinterpret_cast<uint4 *>(c.bulk[r] + off) = o.raw;
+  }
+  // every rank holds all rows once every rank's stores have landed
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = atomicAdd(c.ctl + kCtlBlocks, 1u) == gridDim.x - 1 ? 1 : 0;
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    barrier_signal(c, 1, seq);
+    barrier_wait(c, 1, seq, 22);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      c.ctl[kCtlBlocks] = 0u;
+      c.ctl[kCtlBarrier] = seq;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace
+}  // namespace eb
+
+extern "C" int eb_comm_local_area(eb_comm *c, void **bulk_ptr, size_t *bulk_bytes) {
+  EB_REQUIRE(c && bulk_ptr && bulk_bytes, "comm_local_area: null argument");
+  *bulk_ptr = reinterpret_cast<unsigned char *>(c->recv[c->rank]) + kSignalBytes + c->line_bytes;
+  *bulk_bytes = c->bulk_bytes;
+  return EB_OK;
+}
+
+extern "C" size_t eb_reduce_broadcast_stage_bytes(int world, long long M, int N) {
+  if (world <= 0 || M <= 0 || N <= 0) return 0;
+  return (size_t)world * (size_t)comm_rows_per_rank(M, world) * (size_t)N * 2;
+}
+
+extern "C" int eb_reduce_broadcast(eb_comm *c, long long M, int N, int dtype, size_t stage_offset, size_t gather_offset,
+                                   const void *bias, const void *residual, long long ldr, void *stream) {
+  int rc = check_comm(c, "reduce_broadcast");
+  if (rc) return rc;
+  EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "reduce_broadcast: fp16 or bf16 only");
+  EB_REQUIRE(M > 0 && N > 0 && N % 8 == 0, "reduce_broadcast: N must be a positive multiple of 8");
+  EB_REQUIRE(c->connected, "reduce_broadcast: the context is not connected to its peers yet");
+  const long long rpr = comm_rows_per_rank(M, c->world);
+  const size_t stage = (size_t)c->world * rpr * N * 2, gather = (size_t)M * N * 2;
+  EB_REQUIRE(stage_offset % 256 == 0 && gather_offset % 256 == 0, "reduce_broadcast: offsets must be multiples of 256");
+  if (stage_offset + stage > c->bulk_bytes || gather_offset + gather > c->bulk_bytes)
+    return fail(EB_ELIMIT, "reduce_broadcast: %lld x %d needs %zu + %zu bytes of the bulk region, which has %zu", M, N, stage,
+                gather, c->bulk_bytes);
+  EB_REQUIRE((stage_offset + stage <= gather_offset) || (gather_offset + gather <= stage_offset),
+             "reduce_broadcast: the staging and gather areas overlap");
+  EB_REQUIRE(aligned16(bias) && aligned16(residual) && (!residual || (ldr >= N && ldr % 8 == 0)), "reduce_broadcast: bad bias / residual");
+  const CommDev d = comm_dev(c);
+  const long long total = rpr * (N / 8);
+  const long long want = (total + kRbThreads - 1) / kRbThreads;
+  const int grid = (int)(want < sm_count() ? (want > 0 ? want : 1) : sm_count());
+  cudaStream_t st = as_stream(stream);
+  if (dtype == EB_F16)
+    launch_pdl(reduce_broadcast_kernel<__half>, dim3(grid), dim3(kRbThreads), 0, st, d, M, N, rpr, (unsigned long long)stage_offset,
+               (unsigned long long)gather_offset, reinterpret_cast<const __half *>(bias), reinterpret_cast<const __half *>(residual), ldr);
+  else
+    launch_pdl(reduce_broadcast_kernel<__nv_bfloat16>, dim3(grid), dim3(kRbThreads), 0, st, d, M, N, rpr,
+               (unsigned long long)stage_offset, (unsigned long long)gather_offset, reinterpret_cast<const __nv_bfloat16 *>(bias),
+               reinterpret_cast<const __nv_bfloat16 *>(residual), ldr);
+  return check_launch("reduce_broadcast");
+}
+
 extern "C" int eb_allreduce(eb_comm *c, void *buf, size_t count, int dtype, void *stream) {
   int rc = check_comm(c, "allreduce");
   if (rc) return rc;
@@ -268,9 +447,9 @@ extern "C" int eb_allreduce(eb_comm *c, void *buf, size_t count, int dtype, void
   EB_REQUIRE(buf && (reinterpret_cast<uintptr_t>(buf) & 7u) == 0 && bytes % 8 == 0,
              "allreduce: the buffer must be 8-byte aligned and a multiple of 8 bytes");
   const unsigned long long lines = bytes / 8;
-  if ((unsigned long long)c->world * lines * 16ull > c->recv_bytes / 2)
+  if ((unsigned long long)c->world * lines * 16ull > c->line_bytes / 2)
     return fail(EB_ELIMIT, "allreduce: %zu bytes from %d ranks need %llu bytes per half of the receive area, which has %zu",
-                bytes, c->world, (unsigned long long)c->world * lines * 16ull, c->recv_bytes / 2);
+                bytes, c->world, (unsigned long long)c->world * lines * 16ull, c->line_bytes / 2);
   const CommDev d = comm_dev(c);
   const long long want = (long long)((lines + kArThreads - 1) / kArThreads);
   const int grid = (int)(want < sm_count() ? want : sm_count());

@@ -20,7 +20,9 @@
 
 struct eb_comm {
   int rank, world, device;
-  size_t recv_bytes;                 // one rank's receive area (both halves)
+  size_t line_bytes;                 // flagged-line region of a receive area (both halves)
+  size_t bulk_bytes;                 // bulk region behind it (prompt-sized tensors, plain data)
+  size_t recv_bytes;                 // whole area: signals + line_bytes + bulk_bytes
   void *recv[8];                     // recv[r]: rank r's area as addressable from this process
   bool opened[8];                    // recv[r] came from cudaIpcOpenMemHandle (to be closed)
   bool owns_recv;                    // recv[rank] was allocated by the library
@@ -31,17 +33,26 @@ struct eb_comm {
 
 namespace eb {
 
-constexpr int kCtlEpoch = 0;         // exchanges completed on this rank
-constexpr int kCtlBlocks = 1;        // arrival counter of eb_allreduce's blocks
+constexpr int kCtlEpoch = 0;         // flagged-line exchanges completed on this rank
+constexpr int kCtlBlocks = 1;        // arrival counter of the blocks of the kernel in flight
+constexpr int kCtlBarrier = 2;       // cross-rank barriers completed on this rank (bulk exchanges)
 constexpr int kCtlStatus = 4;        // [4..7]: code, where, block, detail of a wait that ran out
 constexpr size_t kCtlBytes = 256;
+
+// Layout of a receive area: [4 KB of signal words][flagged-line region: two halves][bulk region].
+// Signal words: u32 [2 slots][8 sources]; source s of a cross-rank barrier stores the barrier's
+// sequence number into slot / s of every rank's area and waits until all sources' words in its
+// own area have reached it.
+constexpr size_t kSignalBytes = 4096;
 
 // What a kernel needs of the context (passed by value).
 struct CommDev {
   int rank, world;
-  unsigned char *recv[8];
-  unsigned int *ctl;
-  unsigned long long half_bytes;
+  unsigned char *recv[8];            // flagged-line regions (recv[rank] is local)
+  unsigned char *bulk[8];            // bulk regions
+  unsigned int *sig[8];              // signal words
+  unsigned int *ctl;                 // local control words (never touched by peers)
+  unsigned long long half_bytes;     // one half of a flagged-line region
   unsigned long long wait_budget_ns;
 };
 
@@ -49,9 +60,14 @@ inline CommDev comm_dev(const eb_comm *c) {
   CommDev d{};
   d.rank = c->rank;
   d.world = c->world;
-  for (int r = 0; r < c->world; ++r) d.recv[r] = reinterpret_cast<unsigned char *>(c->recv[r]);
+  for (int r = 0; r < c->world; ++r) {
+    unsigned char *base = reinterpret_cast<unsigned char *>(c->recv[r]);
+    d.sig[r] = reinterpret_cast<unsigned int *>(base);
+    d.recv[r] = base + kSignalBytes;
+    d.bulk[r] = base + kSignalBytes + c->line_bytes;
+  }
   d.ctl = c->ctl;
-  d.half_bytes = c->recv_bytes / 2;
+  d.half_bytes = c->line_bytes / 2;
   d.wait_budget_ns = c->wait_budget_ns;
   return d;
 }
@@ -75,10 +91,36 @@ __device__ __forceinline__ bool ll_load(const void *line, uint32_t seq, uint32_t
   return (uint32_t)(a >> 32) == seq && (uint32_t)(b >> 32) == seq;
 }
 
+// The same load without the test.  Polling code issues ALL the loads of a group first and looks
+// at the sequence numbers afterwards: a test between two loads would make every load wait for
+// the one before it (a full trip to L2 each).
+struct LlLine {
+  unsigned long long a, b;
+  __device__ __forceinline__ bool valid(uint32_t seq) const { return (uint32_t)(a >> 32) == seq && (uint32_t)(b >> 32) == seq; }
+  __device__ __forceinline__ uint32_t d0() const { return (uint32_t)a; }
+  __device__ __forceinline__ uint32_t d1() const { return (uint32_t)b; }
+};
+__device__ __forceinline__ LlLine ll_fetch(const void *line) {
+  LlLine l;
+  asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(l.a), "=l"(l.b) : "l"(line) : "memory");
+  return l;
+}
+
 __device__ __forceinline__ unsigned long long comm_timer() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+
+// Sum over the ranks of a prompt-sized [M, N] 16-bit tensor, in two kernels over the bulk region:
+// the row-parallel GEMM stores the tiles of its partial product straight into the staging area
+// of the rank that owns those rows (rows are dealt out in `world` contiguous blocks of whole
+// 128-row tiles; staging layout [source][row within the block][N]), and a second kernel, after a
+// barrier over the ranks, adds the `world` partials of its own rows (+ bias + residual), stores
+// the finished rows into the gather area [M][N] of every rank and ends with another barrier.
+inline long long comm_rows_per_rank(long long M, int world) {
+  const long long tiles = (M + 127) / 128;
+  return ((tiles + world - 1) / world) * 128;
 }
 
 // Records a wait that ran out in the context's control words (first failure wins).

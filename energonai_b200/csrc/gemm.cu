@@ -75,6 +75,12 @@ struct GemmParams {
   // ranks sent it (see comm.cuh).  A thread's BN batch values of output column n are contiguous
   // in the receive area: lines [source][n][BN / 4].
   CommDev comm;
+  // Normal orientation, reduce-scatter mode (rs != 0): the tile is this rank's partial product of
+  // a row-parallel layer and goes, in the operand type, into the staging area of the rank that
+  // owns its rows (comm.cuh): bulk[owner] + rs_stage_off, layout [source][row in block][N].
+  int rs;
+  long long rs_rpr;
+  unsigned long long rs_stage_off;
   // swap mode, optional: the A operand is the un-normalised input of a LayerNorm whose scale
   // was multiplied into W beforehand.  The kernel computes each row's mean / inverse std over
   // K itself and the last epilogue of a tile evaluates
@@ -555,7 +561,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
       tcgen05_fence_after();
       const uint32_t t_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
 
-      if (!SWAP) {
+      if (!SWAP && p.rs) {
+        // Reduce-scatter mode.  A thread holds one row of the tile, but a store instruction that
+        // writes 32 different rows would cross NVLink as 32 small packets: each warp turns 64
+        // columns of its 32 rows around in shared memory and writes them as 128-byte row
+        // segments (8 lanes x 16 bytes per row, 4 rows per instruction).
+        const long long rpr = p.rs_rpr;
+        const int owner = (int)(s.lane_row0 / rpr);
+        const long long local0 = s.lane_row0 - (long long)owner * rpr + quarter * 32;
+        T *dst = reinterpret_cast<T *>(p.comm.bulk[owner] + p.rs_stage_off) + ((long long)p.comm.rank * rpr + local0) * p.N;
+        constexpr int kPitch = 72;                           // 64 values + 8 of padding per staged row
+        T *stage = reinterpret_cast<T *>(smem + kBarrierBytes + p.stages * ((size_t)kLanes * 128 + (size_t)BN * 128)) +
+                   (size_t)quarter * 32 * kPitch;
+        const int rows_left = p.M - (s.lane_row0 + quarter * 32);
+        for (int c0 = 0; c0 < BN; c0 += 64) {
+          const int n_base = s.col_tile * BN + c0;
+          if (n_base >= p.N) break;                          // warp-uniform
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            float v[16];
+            tmem_ld16(t_base + c0 + cc * 16, v);
+            Vec16<T> lo, hi;
+            float a[8], b[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { a[j] = v[j]; b[j] = v[8 + j]; }
+            lo.pack(a);
+            hi.pack(b);
+            lo.store(stage + lane * kPitch + cc * 16);
+            hi.store(stage + lane * kPitch + cc * 16 + 8);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int row = it * 4 + (lane >> 3), col = (lane & 7) * 8;
+            if (row < rows_left && n_base + col < p.N)
+              *reinterpret_cast<uint4 *>(dst + (long long)row * p.N + n_base + col) =
+                  *reinterpret_cast<const uint4 *>(stage + row * kPitch + col);
+          }
+          __syncwarp();
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+      } else if (!SWAP) {
         // One output row per thread, 16 columns at a time.  The bias and residual of a chunk are
         // requested two chunks ahead (their L2 latency was exposed once per chunk, which made a
         // tile's epilogue as long as its main loop), absent operands are zeros, and the
@@ -755,23 +803,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           }
 #pragma unroll
           for (int m = 0; m < BN; ++m) v[m] = 0.f;
+          // Collect: the lines of kSrc sources at a time are requested together and their
+          // sequence numbers looked at afterwards (a test between two loads would serialise them).
+          constexpr int kSrc = kLines <= 4 ? 4 : (kLines <= 8 ? 2 : 1);
           bool lost = false;
-          for (int r = 0; r < cm.world && !lost; ++r) {
-            const unsigned char *src = cm.recv[cm.rank] + half + ((unsigned long long)r * per_src + (unsigned long long)n * kLines) * 16ull;
-            uint32_t d[BN / 2];
-            uint32_t pending = kLines >= 32 ? 0xffffffffu : (1u << (kLines & 31)) - 1u;
+          for (int r0 = 0; r0 < cm.world && !lost; r0 += kSrc) {
+            LlLine got[kSrc][kLines];
+            const unsigned char *src = cm.recv[cm.rank] + half + ((unsigned long long)r0 * per_src + (unsigned long long)n * kLines) * 16ull;
             unsigned long long t0 = 0;
-            for (unsigned it = 0; pending; ++it) {
+            for (unsigned it = 0;; ++it) {
+              bool all = true;
 #pragma unroll
-              for (int q = 0; q < kLines; ++q)
-                if ((pending >> q) & 1u)
-                  if (ll_load(src + q * 16, comm_seq, d[2 * q], d[2 * q + 1])) pending &= ~(1u << q);
-              if (pending && (it & 63u) == 63u) {
+              for (int j = 0; j < kSrc; ++j)
+                if (r0 + j < cm.world) {
+#pragma unroll
+                  for (int q = 0; q < kLines; ++q) got[j][q] = ll_fetch(src + (unsigned long long)j * per_src * 16ull + q * 16);
+                }
+#pragma unroll
+              for (int j = 0; j < kSrc; ++j)
+                if (r0 + j < cm.world) {
+#pragma unroll
+                  for (int q = 0; q < kLines; ++q) all = all && got[j][q].valid(comm_seq);
+                }
+              if (all) break;
+              if ((it & 63u) == 63u) {
                 if (t0 == 0) t0 = globaltimer();
                 if (*abort_flag || globaltimer() - t0 > cm.wait_budget_ns) {
                   *abort_flag = 1;
                   if (atomicCAS(&g_status[0], 0, EB_ETIMEDOUT) == 0) {
-                    g_status[1] = 6; g_status[2] = blockIdx.x; g_status[3] = r;
+                    g_status[1] = 6; g_status[2] = blockIdx.x; g_status[3] = r0;
                   }
                   lost = true;
                   break;
@@ -779,11 +839,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
               }
             }
 #pragma unroll
-            for (int q = 0; q < BN / 2; ++q) {
-              const float2 f = unpack2<T>(d[q]);
-              v[2 * q] += f.x;
-              v[2 * q + 1] += f.y;
-            }
+            for (int j = 0; j < kSrc; ++j)
+              if (r0 + j < cm.world) {
+#pragma unroll
+                for (int q = 0; q < kLines; ++q) {
+                  const float2 lo = unpack2<T>(got[j][q].d0()), hi = unpack2<T>(got[j][q].d1());
+                  v[4 * q] += lo.x; v[4 * q + 1] += lo.y; v[4 * q + 2] += hi.x; v[4 * q + 3] += hi.y;
+                }
+              }
           }
           if (lost) { alive = false; continue; }
         }
@@ -1148,7 +1211,8 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
                      int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
                      const int32_t *c_row_offset_device, int c_row_offset_limit, int flags, void *workspace,
                      size_t workspace_bytes, void *stream, const eb_comm *comm, const float *ln_colsum = nullptr,
-                     const float *ln_bias = nullptr, double ln_eps = 0.0) {
+                     const float *ln_bias = nullptr, double ln_eps = 0.0, bool reduce_scatter = false,
+                     size_t rs_stage_offset = 0) {
   EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "gemm: operands must be fp16 or bf16 (got dtype %d)", dtype);
   if (ln_colsum || ln_bias) {
     EB_REQUIRE(ln_colsum && ln_bias, "gemm_ln: ln_colsum and ln_bias go together");
@@ -1162,7 +1226,7 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
   EB_REQUIRE(act >= EB_ACT_NONE && act <= EB_ACT_GELU_ERF, "gemm: unknown activation %d", act);
   EB_REQUIRE((flags & ~EB_GEMM_STATIC_W) == 0, "gemm: unknown flag bits 0x%x", flags);
   if (M == 0 || N == 0) return EB_OK;
-  EB_REQUIRE(A && W && C, "gemm: null operand");
+  EB_REQUIRE(A && W && (C || reduce_scatter), "gemm: null operand");
   // the generation orientation (M <= 128) writes C one element at a time: any N will do there
   EB_REQUIRE(K >= 8 && K % 8 == 0 && (N % 8 == 0 || M <= kLanes), "gemm: K, and N for M > 128, must be positive multiples of 8 (K=%d N=%d)", K, N);
   EB_REQUIRE(lda >= K && ldw >= K && lda % 8 == 0 && ldw % 8 == 0, "gemm: lda/ldw must be multiples of 8 and >= K");
@@ -1181,7 +1245,23 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
   p.c_row_offset_dev = c_row_offset_device; p.c_row_limit = c_row_offset_limit;
   p.static_w = (flags & EB_GEMM_STATIC_W) ? 1 : 0;
   p.ln_colsum = ln_colsum; p.ln_bias = ln_bias; p.ln_x = A; p.ln_ldx = lda; p.ln_eps = (float)ln_eps;
-  if (comm && comm->world > 1) {
+  if (reduce_scatter) {
+    int dev = -1;
+    cudaGetDevice(&dev);
+    EB_REQUIRE(comm && comm->connected && comm->device == dev, "gemm_reduce_scatter: the context is not connected or belongs to another device");
+    EB_REQUIRE(M > kLanes, "gemm_reduce_scatter: serves M > 128 (smaller products use eb_gemm_allreduce)");
+    EB_REQUIRE(!bias && !residual && act == EB_ACT_NONE && out_dtype == dtype,
+               "gemm_reduce_scatter: bias, residual and activation belong to eb_reduce_broadcast");
+    p.rs = 1;
+    p.rs_rpr = comm_rows_per_rank(M, comm->world);
+    p.rs_stage_off = rs_stage_offset;
+    const size_t need = (size_t)comm->world * p.rs_rpr * N * 2;
+    EB_REQUIRE(rs_stage_offset % 256 == 0, "gemm_reduce_scatter: the staging offset must be a multiple of 256");
+    if (rs_stage_offset + need > comm->bulk_bytes)
+      return fail(EB_ELIMIT, "gemm_reduce_scatter: %d x %d from %d ranks needs %zu bytes of the bulk region at offset %zu, which has %zu",
+                  M, N, comm->world, need, rs_stage_offset, comm->bulk_bytes);
+    p.comm = comm_dev(comm);
+  } else if (comm && comm->world > 1) {
     int dev = -1;
     cudaGetDevice(&dev);
     EB_REQUIRE(comm->connected && comm->device == dev, "gemm_allreduce: the context is not connected or belongs to another device");
@@ -1241,7 +1321,8 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   p.stages = wide ? 4 : 6;
   p.kpb = 1;
-  const size_t smem = kBarrierBytes + 1024 + (size_t)p.stages * (kLanes * 128 + bn * 128);
+  // (+ 18 KB behind the stages: the staging rows of the reduce-scatter epilogue)
+  const size_t smem = kBarrierBytes + 1024 + (size_t)p.stages * (kLanes * 128 + bn * 128) + (p.rs ? 4 * 32 * 72 * 2 : 0);
   if ((rc = make_map(&tl, A, dtype, M, K, lda, kLanes))) return rc;
   if ((rc = make_map(&tc, W, dtype, N, K, ldw, bn))) return rc;
   if (bn == 256)
@@ -1281,4 +1362,11 @@ extern "C" int eb_gemm_allreduce(const void *A, long long lda, const void *W, lo
   return gemm_impl(A, lda, W, ldw, C, ldc, bias, residual, ldr, M, N, K, dtype, out_dtype, act, c_rows_per_batch,
                    c_batch_stride, c_row_offset_device, c_row_offset_limit, flags, workspace, workspace_bytes, stream,
                    comm);
+}
+
+extern "C" int eb_gemm_reduce_scatter(const void *A, long long lda, const void *W, long long ldw, int M, int N, int K,
+                                      int dtype, int flags, eb_comm *comm, size_t stage_offset, void *stream) {
+  EB_REQUIRE(comm, "gemm_reduce_scatter: null context");
+  return gemm_impl(A, lda, W, ldw, nullptr, N, nullptr, nullptr, 0, M, N, K, dtype, dtype, EB_ACT_NONE, 0, 0, nullptr, 0,
+                   flags, nullptr, 0, stream, comm, nullptr, nullptr, 0.0, true, stage_offset);
 }

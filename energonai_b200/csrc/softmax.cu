@@ -20,7 +20,7 @@ template <typename T, int VEC> struct alignas(sizeof(T) * VEC > 16 ? 16 : sizeof
 
 // VPL = packs cached per lane (0: no caching, re-read).
 template <typename T, int VEC, int VPL>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (VPL * VEC <= 16 ? 4 : (VPL * VEC <= 32 ? 3 : 2)))
 softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int B, int S, int H, int flags,
                float scale) {
   using P = Pack<T, VEC>;
@@ -33,36 +33,48 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
   const int packs_row = S / VEC;   // S % VEC == 0 on this path
   int len = real_len[b];
   len = len < 0 ? 0 : (len > S ? S : len);
-  for (unsigned rb = warp0; rb < rows_b; rb += nwarps) {
-    const int i = (int)(rb % (unsigned)S);
-    const long long row = (long long)b * rows_b + rb;
-    if (i >= len && !(flags & EB_SM_ALLROWS)) continue;
-    int nvis = S;
-    if (flags & EB_SM_CAUSAL) nvis = min(nvis, i + 1);
-    if (flags & EB_SM_KEYLEN) nvis = min(nvis, len);
-    P *rp = reinterpret_cast<P *>(scores + row * S);
-    const int packs_vis = (nvis + VEC - 1) / VEC;
-
-    if (VPL > 0) {
-      // The kernel is bound by instruction issue, not by memory, unless the per-element work is
-      // kept minimal: a pack is converted and scaled once, the keys of the one pack that
-      // straddles the end of the visible prefix are set to -inf there (so the later phases need
-      // no comparisons: exp(-inf - max) is an exact 0), every exponential is evaluated once and
-      // kept in its register, and packs that lie wholly behind the prefix are stored as zeros
-      // without any arithmetic.
+  if (VPL > 0) {
+    // Only rows that are rewritten are walked (query i < real_len unless ALLROWS): live row r of
+    // this batch entry is (head r / live_q, query r % live_q).  With one row at a time the
+    // load -> max -> exp -> sum -> store chain left each warp with memory traffic in flight only
+    // about half of the time, and the kernel ran at half of the copy bandwidth: rows are
+    // pipelined (see the loop below).
+    const unsigned live_q = (flags & EB_SM_ALLROWS) ? (unsigned)S : (unsigned)len;
+    const unsigned live = (unsigned)H * live_q;
+    struct Row { P *rp; int nvis, packs_vis; bool on; };
+    auto locate = [&](unsigned r) {
+      Row w;
+      w.on = r < live;
+      const unsigned rr = w.on ? r : 0u;
+      const unsigned h = live_q ? rr / live_q : 0u;
+      const int i = (int)(rr - h * live_q);
+      int nvis = S;
+      if (flags & EB_SM_CAUSAL) nvis = min(nvis, i + 1);
+      if (flags & EB_SM_KEYLEN) nvis = min(nvis, len);
+      w.nvis = w.on ? nvis : 0;
+      w.packs_vis = (w.nvis + VEC - 1) / VEC;
+      w.rp = reinterpret_cast<P *>(scores + ((long long)b * rows_b + (long long)h * S + i) * S);
+      return w;
+    };
+    // The kernel is bound by instruction issue, not by memory, unless the per-element work is
+    // kept minimal: a pack is converted and scaled once, the keys of the one pack that
+    // straddles the end of the visible prefix are set to -inf there (so the later phases need
+    // no comparisons: exp(-inf - max) is an exact 0), every exponential is evaluated once and
+    // kept in its register, and packs that lie wholly behind the prefix are stored as zeros
+    // without any arithmetic.
+    auto finish = [&](const Row &w, const P (&raw)[VPL > 0 ? VPL : 1]) {
       float x[VPL > 0 ? VPL : 1][VEC];
       float mx = -FLT_MAX;
 #pragma unroll
       for (int t = 0; t < VPL; ++t) {
         const int v = lane + 32 * t;
-        if (v < packs_vis) {
-          const P c = rp[v];
+        if (v < w.packs_vis) {
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) x[t][e] = to_f32<T>(c.e[e]) * scale;
-          if ((v + 1) * VEC > nvis) {
+          for (int e = 0; e < VEC; ++e) x[t][e] = to_f32<T>(raw[t].e[e]) * scale;
+          if ((v + 1) * VEC > w.nvis) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e)
-              if (v * VEC + e >= nvis) x[t][e] = -INFINITY;
+              if (v * VEC + e >= w.nvis) x[t][e] = -INFINITY;
           }
 #pragma unroll
           for (int e = 0; e < VEC; ++e) mx = fmaxf(mx, x[t][e]);
@@ -72,7 +84,7 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
       float sum = 0.f;
 #pragma unroll
       for (int t = 0; t < VPL; ++t) {
-        if (lane + 32 * t < packs_vis) {
+        if (lane + 32 * t < w.packs_vis) {
 #pragma unroll
           for (int e = 0; e < VEC; ++e) {
             x[t][e] = __expf(x[t][e] - mx);
@@ -87,17 +99,47 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
         const int v = lane + 32 * t;
         if (v < packs_row) {
           P out;
-          if (v < packs_vis) {
+          if (v < w.packs_vis) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) out.e[e] = from_f32<T>(x[t][e] * inv);
           } else {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) out.e[e] = from_f32<T>(0.f);
           }
-          rp[v] = out;
+          w.rp[v] = out;
         }
       }
-    } else {
+    };
+    // software pipeline: the packs of the warp's NEXT row are requested before the current row
+    // is reduced, so every warp has loads in flight all the time
+    Row cur = locate(warp0);
+    P raw_cur[VPL > 0 ? VPL : 1];
+#pragma unroll
+    for (int t = 0; t < VPL; ++t)
+      if (lane + 32 * t < cur.packs_vis) raw_cur[t] = cur.rp[lane + 32 * t];
+    for (unsigned r = warp0; r < live; r += nwarps) {
+      const Row nxt = locate(r + nwarps);
+      P raw_nxt[VPL > 0 ? VPL : 1];
+#pragma unroll
+      for (int t = 0; t < VPL; ++t)
+        if (lane + 32 * t < nxt.packs_vis) raw_nxt[t] = nxt.rp[lane + 32 * t];
+      finish(cur, raw_cur);
+      cur = nxt;
+#pragma unroll
+      for (int t = 0; t < VPL; ++t) raw_cur[t] = raw_nxt[t];
+    }
+    return;
+  }
+  for (unsigned rb = warp0; rb < rows_b; rb += nwarps) {
+    const int i = (int)(rb % (unsigned)S);
+    const long long row = (long long)b * rows_b + rb;
+    if (i >= len && !(flags & EB_SM_ALLROWS)) continue;
+    int nvis = S;
+    if (flags & EB_SM_CAUSAL) nvis = min(nvis, i + 1);
+    if (flags & EB_SM_KEYLEN) nvis = min(nvis, len);
+    P *rp = reinterpret_cast<P *>(scores + row * S);
+    const int packs_vis = (nvis + VEC - 1) / VEC;
+    {
       float mx = -FLT_MAX;
       for (int v = lane; v < packs_vis; v += 32) {
         P c = rp[v];

@@ -103,7 +103,7 @@ class MultiHeadAttention1D(nn.Module):
         return tuple(tensor_version(t) for m in mods for t in (m.weight, m.bias) if t is not None)
 
     def forward(self, hidden_states, attention_mask=None, first_cache=False, seq_lens=None, residual=None,
-                kv_state=None, fold_norm=None):
+                kv_state=None, fold_norm=None, transient_ok=False):
         """hidden_states [batch, seq, hidden].  attention_mask: additive, [batch, 1, 1, kv_len]
         (0 / -10000), or None.  With a cache, first_cache=True runs the whole prompt and any
         later call appends the last position.  `residual`, if given, is added to the output
@@ -111,7 +111,8 @@ class MultiHeadAttention1D(nn.Module):
         generation step is captured in a CUDA graph, is a device int32 pair [position, length]
         that the kernels read instead of host values; the cache must already have room.
         `fold_norm` (generation steps only): the LayerNorm1D in front of this module;
-        hidden_states is then its un-normalised input and the QKV GEMM normalises on the fly."""
+        hidden_states is then its un-normalised input and the QKV GEMM normalises on the fly.
+        `transient_ok`: see Linear1D_Row.forward (the block consumes the result at once)."""
         B, S, _ = hidden_states.shape
         hl, d = self.local_hidden, self.attention_head_size
         w, b = self._packed()
@@ -162,4 +163,4 @@ class MultiHeadAttention1D(nn.Module):
                                        scale=self.scaling, q_in_cache=True, kv_len_device=kv_state[1:2])
             ctx = ctx.view(B, 1, hl)
             res = residual[:, -1:, :] if residual is not None else None
-        return self.dense(ctx, residual=res)
+        return self.dense(ctx, residual=res, transient_ok=transient_ok)

@@ -51,10 +51,13 @@ class Block1D(nn.Module):
                 hidden_states = self.attn(hidden_states, attention_mask=attention_mask, first_cache=False,
                                           residual=hidden_states, kv_state=kv_state, fold_norm=self.norm1)
                 return self.mlp(hidden_states, first_cache=True, residual=hidden_states, fold_norm=self.norm2)
+        # Prompt-sized sums of a tensor-parallel group may stay in the exchange's own buffers (two
+        # alternate): the attention output is consumed by norm2 and as the MLP's residual, the
+        # MLP output by the next block's norm1 and residual, both before the buffer comes round.
         normed = self.norm1(hidden_states)
         residual = normed if self.apply_post_layernorm else hidden_states
         hidden_states = self.attn(normed, attention_mask=attention_mask, first_cache=first_cache, residual=residual,
-                                  kv_state=kv_state)
+                                  kv_state=kv_state, transient_ok=True)
         normed = self.norm2(hidden_states)
         residual = normed if self.apply_post_layernorm else hidden_states
-        return self.mlp(normed, first_cache=True, residual=residual)
+        return self.mlp(normed, first_cache=True, residual=residual, transient_ok=True)

@@ -43,10 +43,10 @@ class MLP1D(nn.Module):
         self.act_code = activation_code(activation)
         self.dense_2 = Linear1D_Row(intermediate_dim, hidden_size, bias=bias, dtype=dtype, parallel_input=True)
 
-    def forward(self, hidden_states, first_cache: Optional[bool] = True, residual=None, fold_norm=None):
+    def forward(self, hidden_states, first_cache: Optional[bool] = True, residual=None, fold_norm=None, transient_ok=False):
         """fold_norm: see Linear1D_Col.forward (hidden_states is then the un-normalised input)."""
         if not (self.disable_past_cache or first_cache):
             hidden_states = hidden_states[:, -1:, :]
             residual = residual[:, -1:, :] if residual is not None else None
         inter = self.dense_1(hidden_states, act=self.act_code, fold_norm=fold_norm)
-        return self.dense_2(inter, residual=residual)
+        return self.dense_2(inter, residual=residual, transient_ok=transient_ok)

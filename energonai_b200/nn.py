@@ -85,16 +85,28 @@ class Linear1D_Row(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
 
-    def forward(self, x, residual=None):
+    def forward(self, x, residual=None, transient_ok=False):
         """x is this rank's slice of the input features.  Bias (and an optional residual) enter
-        the sum exactly once: rank 0 adds them in its GEMM epilogue, then the partial products
-        are all-reduced."""
+        the sum exactly once: after the reduction (peer exchange), or in rank 0's GEMM epilogue
+        before an NCCL all-reduce.  transient_ok: the caller consumes the result before the
+        second-next row-parallel call, so a prompt-sized result may stay in the exchange's own
+        buffer instead of being copied out."""
         tp = get_tp()
         x2 = _flat(x)
         if tp.peer is not None and tp.peer.fits(x2.shape[0], self.out_features):
             # generation steps: the all-reduce runs inside the GEMM epilogue over NVLink peer stores
             res = _flat(residual) if residual is not None else None
             y = gemm(x2, self.weight, bias=self.bias, residual=res, static_weight=True, peer=tp.peer)
+            return y.view(*x.shape[:-1], self.out_features)
+        if (tp.peer is not None and x2.dtype in (torch.float16, torch.bfloat16)
+                and tp.peer.fits_bulk(x2.shape[0], self.out_features)):
+            # prompt pass: reduce-scatter inside the GEMM epilogue, then one reduce + broadcast kernel
+            res = _flat(residual) if residual is not None else None
+            if res is not None and res.stride(-1) != 1:
+                res = res.contiguous()
+            y = tp.peer.row_parallel(x2, self.weight, bias=self.bias, residual=res)
+            if not transient_ok:
+                y = y.clone()
             return y.view(*x.shape[:-1], self.out_features)
         lead = tp.rank == 0
         res = _flat(residual) if (residual is not None and lead) else None

@@ -15,22 +15,26 @@ class TPContext:
         self.group, self.rank, self.world_size = group, rank, world_size
         self.peer = None       # PeerExchange for the fused GEMM + all-reduce (enable_peer_exchange)
 
-    def enable_peer_exchange(self, max_rows, max_cols):
+    def enable_peer_exchange(self, max_rows, max_cols, bulk_rows=0):
         """Allocates and maps the NVLink exchange areas (collective over the group).  Row-parallel
-        layers then fuse the all-reduce into the GEMM epilogue for up to max_rows x max_cols
-        outputs (rows <= 128); larger products keep using NCCL."""
+        layers then carry their all-reduce in the library's own kernels: for up to max_rows
+        (<= 128) x max_cols outputs inside the GEMM epilogue or the chained generation step, and,
+        with bulk_rows > 0, for prompt-sized products of up to bulk_rows x max_cols as a
+        reduce-scatter in the GEMM epilogue followed by a reduce-and-broadcast kernel.  Anything
+        larger keeps using NCCL."""
         if self.world_size > 1 and self.peer is None:
             from .comm import PeerExchange
-            self.peer = PeerExchange(self.group, self.rank, self.world_size, max_rows, max_cols)
+            self.peer = PeerExchange(self.group, self.rank, self.world_size, max_rows, max_cols, bulk_rows=bulk_rows)
         return self.peer
 
-    def enable_peer_exchange_for(self, model, max_rows=128):
-        """enable_peer_exchange sized for `model`: the widest row-parallel output it contains."""
+    def enable_peer_exchange_for(self, model, max_rows=128, bulk_rows=8192):
+        """enable_peer_exchange sized for `model`: the widest row-parallel output it contains,
+        and prompts of up to bulk_rows tokens per batch."""
         from .nn import Linear1D_Row
         cols = [m.out_features for m in model.modules() if isinstance(m, Linear1D_Row)]
         if self.world_size <= 1 or not cols:
             return None
-        return self.enable_peer_exchange(max_rows, max(cols))
+        return self.enable_peer_exchange(max_rows, max(cols), bulk_rows=bulk_rows)
 
     def all_reduce(self, t):
         """In-place SUM over the tensor-parallel group (no-op for one rank).  Small CUDA tensors go

@@ -148,16 +148,20 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
  * constructed at energonai/model/attention.py:37 and energonai/model/mlp.py:22).
  *
  * Each rank owns a receive area its peers write into over NVLink with plain stores.  Set-up:
- *   eb_comm_create(rank, world, recv_bytes, NULL, &c)        allocates and zeroes the local area
+ *   eb_comm_create(rank, world, line_bytes, bulk_bytes, NULL, &c)   allocates and zeroes the local area
  *   eb_comm_export_handle(c, blob, n)                        n = eb_comm_handle_bytes()
  *   ... the caller gathers every rank's blob with its own process group, in rank order ...
  *   eb_comm_connect(c, all_blobs, world * n)                 maps the peers' areas (CUDA IPC)
  *   ... a barrier of the caller's: nobody exchanges before everybody is connected ...
  * A caller that maps peer memory itself (one process driving several GPUs, or another symmetric
- * allocator) passes its own area as recv_local and the peers' addresses to
- * eb_comm_connect_pointers instead.  recv_bytes bounds what one exchange may carry:
- * eb_comm_exchange_bytes(world, rows, cols) bytes per HALF of the area for a [rows, cols] 16-bit
+ * allocator) passes its own area (eb_comm_area_bytes(line_bytes, bulk_bytes) bytes, zero-filled)
+ * as recv_local and the peers' addresses to eb_comm_connect_pointers instead.  An area has two
+ * regions.  The flagged-line region (line_bytes) carries generation-step exchanges:
+ * eb_comm_exchange_bytes(world, rows, cols) bytes per HALF of it for a [rows, cols] 16-bit
  * matrix (data travels with a sequence number beside every 4 bytes, so it takes twice its size).
+ * The bulk region (bulk_bytes, may be 0) carries prompt-sized tensors as plain data: the staging
+ * and gather areas of eb_gemm_reduce_scatter / eb_reduce_broadcast, at offsets the caller
+ * chooses; eb_comm_local_area returns its local address so that results can be read in place.
  * All ranks must issue the same exchanges in the same order.  A wait on a peer that lasts longer
  * than the budget (1 s unless changed) is abandoned: the kernel records EB_ETIMEDOUT in the
  * context (eb_comm_status) or in the device status word (eb_device_status), its result is then
@@ -166,7 +170,9 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
 typedef struct eb_comm eb_comm;
 EB_API size_t eb_comm_handle_bytes(void);
 EB_API size_t eb_comm_exchange_bytes(int world, int rows, int cols);
-EB_API int eb_comm_create(int rank, int world, size_t recv_bytes, void *recv_local, eb_comm **out);
+EB_API int eb_comm_create(int rank, int world, size_t line_bytes, size_t bulk_bytes, void *recv_local, eb_comm **out);
+EB_API size_t eb_comm_area_bytes(size_t line_bytes, size_t bulk_bytes);
+EB_API int eb_comm_local_area(eb_comm *comm, void **bulk_ptr, size_t *bulk_bytes);
 EB_API int eb_comm_export_handle(const eb_comm *comm, void *blob, size_t blob_bytes);
 EB_API int eb_comm_connect(eb_comm *comm, const void *all_blobs, size_t all_blobs_bytes);
 EB_API int eb_comm_connect_pointers(eb_comm *comm, void *const *peer_recv);
@@ -174,12 +180,37 @@ EB_API int eb_comm_set_wait_budget(eb_comm *comm, double seconds);
 EB_API int eb_comm_status(eb_comm *comm, int *out4, int clear);
 EB_API int eb_comm_destroy(eb_comm *comm);
 
+/* All-reduce of a prompt-sized row-parallel product in two launches, replacing "F.linear, then
+ * dist.all_reduce, then + bias" of colossalai's Linear1D_Row for M > 128 rows (the layers
+ * constructed at energonai/model/attention.py:37 and energonai/model/mlp.py:22, called with the
+ * whole prompt at attention.py:127-128 and mlp.py:35).
+ *   eb_gemm_reduce_scatter: A [M,K] . W [N,K]^T (this rank's column shard of the weight) on the
+ *     tensor cores; every finished 128-row tile is stored, in the operand type, straight into
+ *     the staging area of the rank that owns those rows (bulk region + stage_offset of that
+ *     rank, over NVLink, 128-byte row segments), so the reduce-scatter half of the all-reduce
+ *     travels while the product is still being computed.  Rows are dealt out in `world`
+ *     contiguous blocks of whole 128-row tiles.
+ *   eb_reduce_broadcast: after a barrier over the ranks, each rank adds the `world` partials of
+ *     its own rows in fp32, in rank order, + bias + residual (rows ldr apart, may be NULL),
+ *     rounds to the operand type and stores the finished rows into the gather area (bulk region
+ *     + gather_offset, [M][N]) of every rank; a second barrier ends the kernel, after which
+ *     every rank reads the complete [M, N] sum at its own eb_comm_local_area + gather_offset.
+ * The staging area takes eb_reduce_broadcast_stage_bytes(world, M, N) bytes, the gather area
+ * M*N*2; offsets are multiples of 256 and the two must not overlap, nor be reused while a peer
+ * may still read them (alternate two gather areas between consecutive calls).  Waits are
+ * bounded (eb_comm_status).  N a multiple of 8, fp16 / bf16. */
+EB_API int eb_gemm_reduce_scatter(const void *A, long long lda, const void *W, long long ldw, int M, int N, int K, int dtype,
+                           int flags, eb_comm *comm, size_t stage_offset, void *stream);
+EB_API int eb_reduce_broadcast(eb_comm *comm, long long M, int N, int dtype, size_t stage_offset, size_t gather_offset,
+                        const void *bias, const void *residual, long long ldr, void *stream);
+EB_API size_t eb_reduce_broadcast_stage_bytes(int world, long long M, int N);
+
 /* In-place SUM of buf[count] (dtype fp32 / fp16 / bf16, sums formed in fp32 in rank order, so
  * every rank holds the bit-identical result) over the ranks of `comm`: each rank stores its
  * buffer into every rank's receive area and adds up what it received ("one-shot": one NVLink
  * crossing, meant for the kilobyte-to-megabyte messages of generation steps; NCCL remains the
  * tool for prompt-sized tensors).  buf 8-byte aligned, count * size a multiple of 8 bytes,
- * world * count * size * 2 <= recv_bytes / 2.  Replaces dist.all_reduce inside Linear1D_Row. */
+ * world * count * size * 2 <= line_bytes / 2.  Replaces dist.all_reduce inside Linear1D_Row. */
 EB_API int eb_allreduce(eb_comm *comm, void *buf, size_t count, int dtype, void *stream);
 
 /* ---- dense layers (tcgen05 tensor-core GEMM) --------------------------------------------- */

@@ -83,11 +83,16 @@ def test_exchange_context_validates_before_any_cuda_call():
     these calls reaches the CUDA runtime."""
     L = _lib.lib()
     out = ctypes.c_void_p()
-    assert L.eb_comm_create(0, 0, 1 << 20, None, ctypes.byref(out)) == -1 and "world" in _lib.last_error()
-    assert L.eb_comm_create(3, 2, 1 << 20, None, ctypes.byref(out)) == -1 and "rank" in _lib.last_error()
-    assert L.eb_comm_create(0, 9, 1 << 20, None, ctypes.byref(out)) == -1
-    assert L.eb_comm_create(0, 2, 1000, None, ctypes.byref(out)) == -1 and "512" in _lib.last_error()
-    assert L.eb_comm_create(0, 2, 1 << 20, None, None) == -1
+    assert L.eb_comm_create(0, 0, 1 << 20, 0, None, ctypes.byref(out)) == -1 and "world" in _lib.last_error()
+    assert L.eb_comm_create(3, 2, 1 << 20, 0, None, ctypes.byref(out)) == -1 and "rank" in _lib.last_error()
+    assert L.eb_comm_create(0, 9, 1 << 20, 0, None, ctypes.byref(out)) == -1
+    assert L.eb_comm_create(0, 2, 1000, 0, None, ctypes.byref(out)) == -1 and "512" in _lib.last_error()
+    assert L.eb_comm_create(0, 2, 1 << 20, 100, None, ctypes.byref(out)) == -1 and "bulk" in _lib.last_error()
+    assert L.eb_comm_create(0, 2, 1 << 20, 0, None, None) == -1
+    assert L.eb_comm_area_bytes(1 << 20, 1 << 20) == 4096 + (2 << 20)
+    assert L.eb_reduce_broadcast_stage_bytes(8, 8192, 5120) == 8 * 1024 * 5120 * 2
+    assert L.eb_reduce_broadcast(None, 256, 64, _lib.F16, 0, 0, None, None, 0, None) == -1
+    assert L.eb_gemm_reduce_scatter(None, 8, None, 8, 256, 64, 64, _lib.F16, 0, None, 0, None) == -1
     assert out.value is None
     assert L.eb_comm_handle_bytes() == 64
     assert L.eb_comm_exchange_bytes(8, 16, 5120) == 8 * 16 * 5120 * 4

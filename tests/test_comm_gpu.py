@@ -15,16 +15,18 @@ from test_gemm_gpu import reference, check_close, status_ok
 
 pytestmark = pytest.mark.gpu
 
-AREA = 8 << 20
+LINES = 8 << 20                      # flagged-line region of the test contexts
+SIGNALS = 4096                       # signal words in front of it (csrc/comm.cuh)
 
 
-def make_ctx(world=2, budget=None):
+def make_ctx(world=2, budget=None, bulk=0):
     """Rank 0 of `world` over two local buffers: its own receive area and one that stands for
-    every peer's."""
+    every peer's.  Area = signal words | flagged-line region | bulk region."""
     from energonai_b200.comm import PeerExchange
-    mine = torch.zeros(AREA, dtype=torch.uint8, device="cuda")
-    peer = torch.zeros(AREA, dtype=torch.uint8, device="cuda")
-    ctx = PeerExchange.from_pointers(0, world, mine, [mine.data_ptr()] + [peer.data_ptr()] * (world - 1), wait_budget_s=budget)
+    mine = torch.zeros(SIGNALS + LINES + bulk, dtype=torch.uint8, device="cuda")
+    peer = torch.zeros(SIGNALS + LINES + bulk, dtype=torch.uint8, device="cuda")
+    ctx = PeerExchange.from_pointers(0, world, mine, [mine.data_ptr()] + [peer.data_ptr()] * (world - 1), line_bytes=LINES,
+                                     wait_budget_s=budget)
     return ctx, mine, peer
 
 
@@ -39,12 +41,12 @@ def pack_lines(values16, seq):
 
 
 def write_lines(area, half, first_line, lines_u32):
-    off = half * (AREA // 2) + first_line * 16
+    off = SIGNALS + half * (LINES // 2) + first_line * 16
     area[off:off + lines_u32.size * 4] = torch.from_numpy(lines_u32.view(np.uint8)).cuda()
 
 
 def read_payload16(area, half, first_line, n_lines):
-    off = half * (AREA // 2) + first_line * 16
+    off = SIGNALS + half * (LINES // 2) + first_line * 16
     raw = area[off:off + n_lines * 16].cpu().numpy().view(np.uint32).reshape(-1, 4)
     return raw[:, [0, 2]].copy().view(np.uint16).reshape(-1), raw[:, 1], raw[:, 3]
 
@@ -56,7 +58,7 @@ def as_u16(t):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 def test_allreduce_single_rank_is_identity_and_advances(dtype):
     from energonai_b200.comm import PeerExchange
-    area = torch.zeros(AREA, dtype=torch.uint8, device="cuda")
+    area = torch.zeros(SIGNALS + LINES, dtype=torch.uint8, device="cuda")
     ctx = PeerExchange.from_pointers(0, 1, area, [area.data_ptr()])
     x = torch.randn(3000, device="cuda").to(dtype)
     want = x.clone()
@@ -103,7 +105,7 @@ def test_allreduce_gives_up_when_the_peer_never_writes():
 
 def test_limits_are_refused():
     ctx, mine, peer = make_ctx()
-    big = torch.zeros(AREA, device="cuda", dtype=torch.float16)
+    big = torch.zeros(LINES, device="cuda", dtype=torch.float16)
     with pytest.raises(RuntimeError, match="receive area"):
         ctx.all_reduce(big)
     with pytest.raises(RuntimeError, match="8"):
@@ -177,7 +179,7 @@ def test_chain_with_exchanged_products(M, h, f, v, world, dtype):
     g = torch.Generator(device="cuda").manual_seed(M * 3 + h + world)
     t = layer_tail(g, M, h, f, v, dtype)
     if world == 1:
-        area = torch.zeros(AREA, dtype=torch.uint8, device="cuda")
+        area = torch.zeros(SIGNALS + LINES, dtype=torch.uint8, device="cuda")
         ctx = PeerExchange.from_pointers(0, 1, area, [area.data_ptr()])
         mine = area
     else:
@@ -237,4 +239,72 @@ def test_chain_exchange_gives_up_when_the_peer_never_writes():
     code, where, _, _ = device_status()
     assert code == -4 and where == 10
     assert device_status()[0] == 0
+    ctx.destroy()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("world", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 128), (1000, 1024, 640), (2048, 5120, 640), (300, 264, 2560)])
+def test_prompt_sized_row_parallel_sum(M, N, K, world, dtype):
+    """eb_gemm_reduce_scatter + eb_reduce_broadcast as rank 0.  world 1: the whole sum lands in the
+    gather area.  world 2: the test plays rank 1: it writes rank 1's partial of rank 0's rows into
+    rank 0's staging area and pre-sets the two barrier words; afterwards rank 0's rows of the
+    gather areas of BOTH ranks hold own + peer + bias + residual, and the tiles of the rows rank 1
+    owns have arrived in rank 1's staging area.  Staging layout: [source][row in block][N]; rows
+    are dealt out in blocks of whole 128-row tiles."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K + world)
+    a = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(dtype)
+    bias = torch.randn(N, device="cuda", generator=g).to(dtype)
+    res = torch.randn(M, N, device="cuda", generator=g).to(dtype)
+    rpr = -(-(-(-M // 128)) // world) * 128                  # rows per rank: whole 128-row tiles
+    bulk = (3 * max(world * rpr, M) * N * 2 + 4096) // 512 * 512
+    own = (a.float() @ w.float().t())
+    if world == 1:
+        from energonai_b200.comm import PeerExchange
+        area = torch.zeros(SIGNALS + LINES + bulk, dtype=torch.uint8, device="cuda")
+        ctx = PeerExchange.from_pointers(0, 1, area, [area.data_ptr()], line_bytes=LINES)
+        for _ in range(3):                                    # gather areas alternate, barrier numbers advance
+            out = ctx.row_parallel(a, w, bias=bias, residual=res)
+            torch.cuda.synchronize()
+            assert ctx.status()[0] == 0
+            close_after_exchange(out, own.to(dtype).float() + bias.float() + res.float(), own, dtype)
+        ctx.destroy()
+        return
+    ctx, mine, peer = make_ctx(bulk=bulk)
+    other = (torch.randn(rpr, N, device="cuda", generator=g) * 2).to(dtype)       # rank 1's partial of rank 0's rows
+    stage_b = (world * rpr * N * 2 + 511) // 512 * 512
+    gather_b = (M * N * 2 + 511) // 512 * 512
+    B0 = SIGNALS + LINES                                                         # start of the bulk region
+    for call in (1, 2):
+        mine[B0 + rpr * N * 2: B0 + 2 * rpr * N * 2] = other.view(torch.uint8).view(-1)     # staging slot of source 1
+        sig = mine[:64].view(torch.int32)
+        sig[1] = call                                                             # slot 0 (start barrier), source 1
+        sig[8 + 1] = call                                                         # slot 1 (end barrier), source 1
+        out = ctx.row_parallel(a, w, bias=bias, residual=res)
+        torch.cuda.synchronize()
+        assert ctx.status()[0] == 0
+        mine_rows = min(rpr, M)
+        want = own[:mine_rows].to(dtype).float() + other[:mine_rows].float() + bias.float() + res[:mine_rows].float()
+        close_after_exchange(out[:mine_rows], want, own[:mine_rows], dtype)
+        goff = B0 + stage_b + (call - 1) * gather_b
+        sent = peer[goff: goff + mine_rows * N * 2].view(dtype).view(mine_rows, N)
+        assert torch.equal(sent, out[:mine_rows])                                 # the same rows went to the peer
+        if M > rpr:                                                               # tiles of the peer's rows, in ITS staging slot 0
+            theirs = peer[B0: B0 + (M - rpr) * N * 2].view(dtype).view(M - rpr, N)
+            from test_gemm_gpu import check_close
+            check_close(theirs, own[rpr:], dtype)
+        psig = peer[:64].view(torch.int32)
+        assert int(psig[0]) == call and int(psig[8]) == call                      # rank 0 announced itself at both barriers
+    ctx.destroy()
+
+
+def test_bulk_barrier_gives_up_when_the_peer_never_arrives():
+    ctx, mine, peer = make_ctx(budget=0.005, bulk=8 << 20)
+    a = torch.randn(256, 128, device="cuda").half()
+    w = torch.randn(256, 128, device="cuda").half()
+    ctx.row_parallel(a, w)
+    torch.cuda.synchronize()
+    code, where, _, detail = ctx.status()
+    assert code == -4 and where in (21, 22) and detail == 1
     ctx.destroy()

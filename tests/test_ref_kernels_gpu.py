@@ -8,7 +8,7 @@ sequence length <= 1024 for the softmax (one thread per key), heads * head_dim <
 2048 (fp16) for the FT transposes, int32 lengths, fp32 / fp16 only (LayerNorm also bf16).
 
 Tolerances: copies and index work bit-exact; softmax 2e-6 (fp32) / one fp16 rounding 1e-3
-(both sides use the fast-math exponential); LayerNorm one rounding of the output type.
+(both sides use the fast-math exponential); LayerNorm one step of the output type.
 The last test times both sides per kernel and writes the table the profiles quote."""
 import ctypes
 import os
@@ -77,9 +77,11 @@ def test_layer_norm_against_the_reference_kernel(ref, n1, n2, dtype):
     torch.cuda.synchronize()
     assert float((mean - mean_ref).abs().max()) <= 2e-5 * (1 + float(mean_ref.abs().max()))
     assert float(((iv - iv_ref) / iv_ref).abs().max()) <= 2e-5
-    ulp = {torch.float32: 2e-6, torch.float16: 2 ** -10, torch.bfloat16: 2 ** -7}[dtype]
+    # both sides round the same fp32 value up to the last bits of the statistics: outputs may
+    # differ by one step of the output type (2^-10 / 2^-7 of the next power of two for fp16 / bf16)
+    step = {torch.float32: 4e-6, torch.float16: 2 ** -9, torch.bfloat16: 2 ** -6}[dtype]
     err = (y.float() - y_ref.float()).abs()
-    assert bool((err <= ulp * y_ref.float().abs() + ulp).all()), float(err.max())
+    assert bool((err <= step * y_ref.float().abs() + step / 4).all()), float(err.max())
 
 
 def fixture(dtype, B=8, S=128, H=12, D=64, lens=LENS):

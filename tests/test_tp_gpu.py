@@ -28,7 +28,7 @@ def _worker(rank, world, port, ret, use_peer=False):
         ctx = tp.init_tp(world)
         h, H, f, B, S = 512, 8, 2048, 3, 40
         if use_peer:
-            ctx.enable_peer_exchange(16, 5120)
+            ctx.enable_peer_exchange(16, 5120, bulk_rows=512)
             assert ctx.peer is not None
         gen = torch.Generator().manual_seed(9)
         bp = inputs.block_params(gen, h, f, rich=True, std=0.04)
@@ -113,7 +113,7 @@ def _model_worker(rank, world, port, ret, use_peer=False):
         want = full(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1, record=record)
         ctx = tp.init_tp(world)
         if use_peer:
-            ctx.enable_peer_exchange(16, 256)
+            ctx.enable_peer_exchange(16, 5120, bulk_rows=512)
             # the stand-alone one-shot all-reduce against NCCL, several sizes and dtypes
             for dt, n in ((torch.float16, 4096), (torch.bfloat16, 1024 * 40), (torch.float32, 20)):
                 t = (torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rank)) * 3).to(dt)
