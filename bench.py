@@ -1,6 +1,6 @@
 """Benchmark of the tensor-parallel transformer layer path: OPT-13B-shaped fp16 generation.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config 2|3|4|5]
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
 
 One "step" = one pass of the hot path over one batch: the prompt pass (batch 16, 512
@@ -13,6 +13,11 @@ Besides timing, the run verifies what it timed (outside the timed region): all r
 hold identical tokens, no bounded device-side wait may have run out, and a two-layer model of
 the same layer shape, sharded the same way, must reproduce the CPU oracle's greedy tokens and
 final hidden states ("check" in the line).
+
+`--config` selects another of the benchmark configurations (4: GPT-3-175B-shaped layer slab,
+5: OPT-66B bucket-batched decode with p50 / p99 step latency, 2: the BERT-large encoder block
+assembled from the padding / softmax / LayerNorm kernel API); the default, 3, is the one the
+headline metric is quoted on.
 
 `--impl reference` times the reference's own algorithm for this path (its PyTorch layer
 forward, restated in oracle/layers.py) on the host CPU cores, on a bounded sample of the
@@ -31,9 +36,24 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-CFG = dict(name="OPT-13B", hidden=5120, heads=40, ffn=20480, depth=40, vocab=50272, max_pos=2050,
-           batch=16, prompt=512, new_tokens=128, len_lo=256)
-METRIC = "OPT-13B fp16 tokens/s (prefill+decode)"
+# The benchmark configurations of BASELINE.json.  3 is the one the headline metric is quoted on and
+# the default; 4 and 5 reuse the same generation harness; 2 is the encoder block assembled from
+# the kernel API the way the reference's BERT example does it.
+CONFIGS = {
+    3: dict(kind="generation", name="OPT-13B", hidden=5120, heads=40, ffn=20480, depth=40, vocab=50272, max_pos=2050,
+            batch=16, prompt=512, new_tokens=128, len_lo=256, act="relu", fused_qkv=False, dtype="fp16",
+            metric="OPT-13B fp16 tokens/s (prefill+decode)"),
+    4: dict(kind="generation", name="GPT-3-175B layer slab", hidden=12288, heads=96, ffn=49152, depth=8, vocab=50272,
+            max_pos=2050, batch=8, prompt=1024, new_tokens=1024, len_lo=1024, act="gelu_tanh", fused_qkv=True, dtype="fp16",
+            metric="GPT-3-175B-shaped 8-layer slab fp16 tokens/s (prefill 1024 + decode to 2048)"),
+    5: dict(kind="generation", name="OPT-66B", hidden=9216, heads=72, ffn=36864, depth=64, vocab=50272, max_pos=2560,
+            requests=64, len_lo=32, len_hi=2048, bucket=256, new_tokens=256, act="relu", fused_qkv=False, dtype="bf16",
+            metric="OPT-66B bf16 bucket-batched decode tokens/s (64 requests, 256 steps)"),
+    2: dict(kind="encoder_block", name="BERT-large block", hidden=1024, heads=16, ffn=4096, batch=32, seq=512, len_lo=32,
+            dtype="fp16", metric="BERT-large encoder block fp16 tokens/s (packed, padding kernels + scale_mask_softmax + LayerNorm)"),
+}
+CFG = CONFIGS[3]
+METRIC = CFG["metric"]
 
 
 def measured_peaks():
@@ -100,7 +120,7 @@ def cpu_sample(cfg, decode_steps=3):
     x = torch.randn(B, S + decode_steps, cfg["hidden"], generator=gen)
     lens = torch.randint(cfg["len_lo"], S + 1, (B,), generator=gen)
     mask = (torch.arange(S)[None, :] >= (S - lens)[:, None]).float()
-    blk = layers.OracleBlock(bp, cfg["heads"], "relu")
+    blk = layers.OracleBlock(bp, cfg["heads"], cfg.get("act", "relu"))
     with torch.inference_mode():
         t0 = time.perf_counter()
         blk(x[:, :S], (1.0 - mask.view(B, 1, 1, S)) * -10000.0, True)
@@ -123,38 +143,64 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    cfg = CONFIGS[args.config]
+    if cfg["kind"] != "generation" or args.config == 5:
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm is implemented for configurations 3 and 4 only"}), flush=True)
+        return
     for _ in range(args.warmup):
-        cpu_sample(CFG, decode_steps=1)
+        cpu_sample(cfg, decode_steps=1)
     vals, jobs = [], []
     for _ in range(args.steps):
-        v, sample, cores, t_job = cpu_sample(CFG)
+        v, sample, cores, t_job = cpu_sample(cfg)
         vals.append(v)
         jobs.append(t_job)
     value = statistics.mean(vals)
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+    line = {"impl": "reference", "metric": cfg["metric"], "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": statistics.mean(jobs) * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(args.gpus),
+            "config": workload_config(cfg, args.gpus),
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus):
-    c = CFG
-    return {"workload": f"{c['name']}-shaped decoder, random init: {c['depth']} layers, hidden {c['hidden']}, "
-                        f"{c['heads']} heads, FFN {c['ffn']} ReLU; batch {c['batch']}, prompts left-padded to "
-                        f"{c['prompt']} (true lengths uniform in [{c['len_lo']},{c['prompt']}]), prompt pass + "
-                        f"{c['new_tokens']} greedy steps with KV cache",
-            "global_batch": c["batch"], "seq_len": c["prompt"], "new_tokens": c["new_tokens"],
-            "parallelism": f"tp{n_gpus}", "l2": "inputs larger than L2 (26 GB of weights stream every step)"}
+def workload_config(c, n_gpus):
+    if c["kind"] == "encoder_block":
+        return {"workload": f"{c['name']}, random init: hidden {c['hidden']}, {c['heads']} heads, FFN {c['ffn']} GELU, post-LN; batch "
+                            f"{c['batch']}, lengths uniform in [{c['len_lo']},{c['seq']}] right-padded to {c['seq']}, key mask; "
+                            "padding removed / rebuilt around the block with the FT kernels, scale_mask_softmax (scale 1/8), LayerNorm",
+                "global_batch": c["batch"], "seq_len": c["seq"], "parallelism": f"tp{n_gpus}",
+                "l2": "eight activation sets are cycled (each timed pass touches > 126 MB before a buffer is reused)"}
+    if "requests" in c:
+        shape = (f"{c['requests']} requests, prompt lengths log-uniform in [{c['len_lo']},{c['len_hi']}], grouped into buckets of "
+                 f"{c['bucket']} and left-padded per bucket; every bucket runs its prompt pass + {c['new_tokens']} greedy steps")
+        batch, seq = c["requests"], c["len_hi"]
+    else:
+        shape = (f"batch {c['batch']}, prompts left-padded to {c['prompt']} (true lengths uniform in [{c['len_lo']},{c['prompt']}]), "
+                 f"prompt pass + {c['new_tokens']} greedy steps with KV cache")
+        batch, seq = c["batch"], c["prompt"]
+    return {"workload": f"{c['name']}-shaped decoder, random init: {c['depth']} layers, hidden {c['hidden']}, {c['heads']} heads, "
+                        f"FFN {c['ffn']} {c['act']}; {shape}",
+            "global_batch": batch, "seq_len": seq, "new_tokens": c["new_tokens"], "parallelism": f"tp{n_gpus}",
+            "l2": "inputs larger than L2 (the weights stream from HBM every step)"}
 
 
 # ------------------------------------------------------------------------------------------------
-# GPU arm
+# GPU arm: generation (configurations 3, 4, 5)
 # ------------------------------------------------------------------------------------------------
-def build_model(cfg, dtype, world):
+def torch_dtype(cfg):
+    import torch
+    return torch.float16 if cfg["dtype"] == "fp16" else torch.bfloat16
+
+
+def activation_of(cfg):
+    import torch
+    from energonai_b200.model.mlp import gelu_impl
+    return torch.nn.functional.relu if cfg["act"] == "relu" else gelu_impl
+
+
+def build_model(cfg, world):
     import torch
     from energonai_b200.model import create_pipeline_model
     torch.manual_seed(1234)          # same seed on every rank: replicated parameters agree
@@ -163,25 +209,53 @@ def build_model(cfg, dtype, world):
         # largest factory, model_factory.py:352): every rank streams 1/N of the LM head per step
         model = create_pipeline_model(depth=cfg["depth"], vocab_size=cfg["vocab"], hidden_size=cfg["hidden"],
                                       max_seq_len=cfg["max_pos"], num_heads=cfg["heads"],
-                                      mlp_ratio=cfg["ffn"] / cfg["hidden"], activation=torch.nn.functional.relu,
-                                      is_decoder=True, fused_qkv=False, dtype=dtype, vocab_parallel=world > 1)
+                                      mlp_ratio=cfg["ffn"] / cfg["hidden"], activation=activation_of(cfg),
+                                      is_decoder=True, fused_qkv=cfg["fused_qkv"], dtype=torch_dtype(cfg),
+                                      vocab_parallel=world > 1)
     with torch.no_grad():
         model.embed.word_embeddings.weight.normal_(0, 0.02)
         model.embed.position_embeddings.weight.normal_(0, 0.02)
     return model.eval()
 
 
-def step_bytes(cfg, world, kv_len):
+def make_batches(cfg):
+    """[(input_ids, attention_mask, target_len)] on the host (pinned).  One batch, or one per
+    length bucket (configuration 5: the reference's serving example batches requests of similar
+    length and left-pads them, examples/opt/batch.py:31-53)."""
+    import torch
+    from oracle import inputs   # seeded prompt generator only (no oracle compute on the timed path)
+    if "requests" not in cfg:
+        ids, mask, _ = inputs.left_padded_prompts(0, cfg["batch"], cfg["prompt"], cfg["len_lo"], cfg["prompt"], cfg["vocab"])
+        return [(ids.pin_memory(), mask.pin_memory(), cfg["prompt"] + cfg["new_tokens"])]
+    gen = torch.Generator().manual_seed(0)
+    import math
+    u = torch.rand(cfg["requests"], generator=gen)
+    lens = torch.exp(math.log(cfg["len_lo"]) + u * (math.log(cfg["len_hi"]) - math.log(cfg["len_lo"]))).round().long()
+    lens = lens.clamp(cfg["len_lo"], cfg["len_hi"])
+    out = []
+    for top in range(cfg["bucket"], cfg["len_hi"] + 1, cfg["bucket"]):
+        sel = lens[(lens > top - cfg["bucket"]) & (lens <= top)]
+        if sel.numel() == 0:
+            continue
+        B = sel.numel()
+        ids = torch.randint(2, cfg["vocab"], (B, top), generator=gen)
+        valid = torch.arange(top)[None, :] >= (top - sel)[:, None]
+        ids = torch.where(valid, ids, torch.ones_like(ids))
+        out.append((ids.pin_memory(), valid.float().pin_memory(), top + cfg["new_tokens"]))
+    return out
+
+
+def step_bytes(cfg, world, batch, kv_len):
     """Algorithmic bytes one generation step moves on ONE rank: this rank's weight shards, its
     slice of the cached keys and values, the LM head it streams."""
     h, f, e = cfg["hidden"], cfg["ffn"], 2
     weights = cfg["depth"] * (4 * h * h + 2 * h * f) * e / world
-    kv = cfg["depth"] * 2 * cfg["batch"] * kv_len * h * e / world
+    kv = cfg["depth"] * 2 * batch * kv_len * h * e / world
     head = cfg["vocab"] * h * e / world
     return weights + kv + head
 
 
-def probe_decode_kernels(model, cfg, st, world):
+def probe_decode_kernels(model, cfg, st, world, batch):
     """Average device time per launch of the dominant generation-step kernel, launched with the
     step's real arguments (folded LayerNorms, bias, residual, cache-row mapping, the exchange of
     a tensor-parallel group), back to back, each layer on its own weights (nothing is
@@ -191,8 +265,10 @@ def probe_decode_kernels(model, cfg, st, world):
     residual for out-proj / FC2).  Tensor-parallel group: the chained launches of the step (one
     per layer: out-proj, exchange, FC1, FC2, exchange, QKV).  Returns a dict."""
     import torch
-    B, h = cfg["batch"], cfg["hidden"]
+    B, h = batch, cfg["hidden"]
     dt = model.norm.module.weight.dtype
+    tname = "__half" if dt == torch.float16 else "__nv_bfloat16"
+    bn = 16 if B <= 16 else 32 if B <= 32 else 64 if B <= 64 else 128
     e = 2
     if st.get("chains"):
         chains = st["chains"]
@@ -202,25 +278,31 @@ def probe_decode_kernels(model, cfg, st, world):
                 ch.run()
         n_launch = len(chains)
         nbytes = cfg["depth"] * (4 * h * h + 2 * h * cfg["ffn"]) * e / world + cfg["vocab"] * h * e / world
-        name = "chain_kernel<__half, 16> (one launch per layer: out-proj, exchange + LayerNorm, FC1, FC2, exchange + LayerNorm, QKV)"
+        name = f"chain_kernel<{tname}, {bn}> (one launch per layer: out-proj, exchange + LayerNorm, FC1, FC2, exchange + LayerNorm, QKV)"
     else:
         from energonai_b200.gemm import gemm
+        from energonai_b200.nn import can_fold
         x = torch.randn(B, 1, h, device="cuda", dtype=dt)
         kv_state = st["kv_state"]
+        fold = can_fold(B, dt, model.blocks[0].fold_layernorm) and not model.blocks[0].apply_post_layernorm
         jobs = []
         nbytes = 0
         for blk in model.blocks:
             at, mlp = blk.attn, blk.mlp
             w, b = at._packed()
-            w_f, colsum, bias32, eps = at._fold.get(w, b, blk.norm1, at._param_versions())
             buf = at.past_cache.buf
             ctx = torch.randn(B, 1, at.local_hidden, device="cuda", dtype=dt)
-            jobs.append(lambda w_f=w_f, colsum=colsum, bias32=bias32, eps=eps, buf=buf: gemm(
-                x[:, 0], w_f, static_weight=True, out=buf, out_rows_per_batch=1, out_batch_stride=buf.stride(0),
-                out_ld=buf.stride(1), out_row_offset_device=kv_state[0:1], out_row_limit=buf.shape[1],
-                ln_fold=(colsum, bias32, eps)))
-            jobs.append(lambda at=at, ctx=ctx: at.dense(ctx, residual=x))
-            jobs.append(lambda mlp=mlp, blk=blk: mlp.dense_1(x, act=mlp.act_code, fold_norm=blk.norm2))
+            kw = dict(static_weight=True, out=buf, out_rows_per_batch=1, out_batch_stride=buf.stride(0), out_ld=buf.stride(1),
+                      out_row_offset_device=kv_state[0:1], out_row_limit=buf.shape[1])
+            if fold:
+                w_f, colsum, bias32, eps = at._fold.get(w, b, blk.norm1, at._param_versions())
+                jobs.append(lambda w_f=w_f, c=colsum, b32=bias32, eps=eps, kw=kw: gemm(x[:, 0], w_f, ln_fold=(c, b32, eps), **kw))
+                jobs.append(lambda at=at, ctx=ctx: at.dense(ctx, residual=x))
+                jobs.append(lambda mlp=mlp, blk=blk: mlp.dense_1(x, act=mlp.act_code, fold_norm=blk.norm2))
+            else:
+                jobs.append(lambda w=w, b=b, kw=kw: gemm(x[:, 0], w, bias=b, **kw))
+                jobs.append(lambda at=at, ctx=ctx: at.dense(ctx, residual=x))
+                jobs.append(lambda mlp=mlp: mlp.dense_1(x, act=mlp.act_code))
             inter = torch.randn(B, 1, mlp.dense_1.out_per_rank, device="cuda", dtype=dt)
             jobs.append(lambda mlp=mlp, inter=inter: mlp.dense_2(inter, residual=x))
             for wt, k_in in ((w, h), (at.dense.weight, at.local_hidden), (mlp.dense_1.weight, h),
@@ -231,7 +313,8 @@ def probe_decode_kernels(model, cfg, st, world):
             for j in jobs:
                 j()
         n_launch = len(jobs)
-        name = "gemm_kernel<__half, 16, true> (generation-step GEMM, M = batch 16; QKV / FC1 with the LayerNorm folded in)"
+        name = (f"gemm_kernel<{tname}, {bn}, true> (generation-step GEMM, M = batch {B}" +
+                ("; QKV / FC1 with the LayerNorm folded in)" if fold else ")"))
     run()
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
@@ -250,7 +333,7 @@ def probe_decode_kernels(model, cfg, st, world):
     return {"kernel": name, "bytes": nbytes, "ms": ms, "launches": n_launch}
 
 
-def exposed_exchange(model, cfg, ids_d, mask_d, tgt, prefill_ms, step_ms):
+def exposed_exchange(model, ids_d, mask_d, tgt, prefill_ms, step_ms):
     """How much of the prompt pass and of the generation step is spent waiting for the other
     ranks: the same shards, shapes and launches are timed once more with the exchange reduced to
     this rank alone (a context of one rank that exchanges with itself; NCCL all-reduces skipped),
@@ -258,14 +341,13 @@ def exposed_exchange(model, cfg, ids_d, mask_d, tgt, prefill_ms, step_ms):
     exposed fraction = (time with the exchange - time without) / time with."""
     import torch
     from energonai_b200 import tp
+    from energonai_b200._lib import lib
     from energonai_b200.comm import PeerExchange
     ctx = tp.get_tp()
     real_peer, real_all_reduce, real_gather = ctx.peer, ctx.all_reduce, ctx.all_gather_last_dim
-    from energonai_b200._lib import lib
     line_b, bulk_b = (real_peer.line_bytes, real_peer.bulk_bytes) if real_peer is not None else (1 << 20, 0)
     area = torch.zeros(lib().eb_comm_area_bytes(line_b, bulk_b), dtype=torch.uint8, device="cuda")
     solo = PeerExchange.from_pointers(0, 1, area, [area.data_ptr()], line_bytes=line_b)
-    solo.max_rows, solo.max_cols = cfg["batch"], cfg["hidden"]
     saved_state = model._decode_state
     try:
         if real_peer is not None:
@@ -273,9 +355,9 @@ def exposed_exchange(model, cfg, ids_d, mask_d, tgt, prefill_ms, step_ms):
         ctx.all_reduce = lambda t: t
         ctx.all_gather_last_dim = lambda t: torch.cat([t] * ctx.world_size, dim=-1)
         model._decode_state = None
+        model(input_ids=ids_d, attention_mask=mask_d, max_tokens=tgt, top_k=1, record={"allow_graph": True})
         rec = {"allow_graph": True}
         model(input_ids=ids_d, attention_mask=mask_d, max_tokens=tgt, top_k=1, record=rec)
-        model(input_ids=ids_d, attention_mask=mask_d, max_tokens=tgt, top_k=1, record=(rec := {"allow_graph": True}))
         torch.cuda.synchronize()
         ev = rec["step_events"]
         solo_prefill = ev[0].elapsed_time(ev[1])
@@ -294,14 +376,12 @@ def exposed_exchange(model, cfg, ids_d, mask_d, tgt, prefill_ms, step_ms):
     return out
 
 
-def verify(world, rank, out_tokens):
+def verify(cfg, world, rank, out_tokens, with_oracle):
     """Checks on what was timed, outside the timed region.  Returns a dict for the line."""
     import torch
     import torch.distributed as dist
     from energonai_b200 import tp
     from energonai_b200.gemm import device_status
-    from energonai_b200.sharding import shard_model_state
-    from oracle import inputs, layers      # the checker (never on the timed path)
     res = {}
     problems = []
     tok = out_tokens.contiguous()
@@ -319,18 +399,37 @@ def verify(world, rank, out_tokens):
         dist.all_reduce(bad)
     if float(bad) > 0:
         problems.append(f"a device-side wait ran out or a limit was hit on some rank (this rank: {st}, {cst})")
+    if with_oracle:
+        problems += verify_against_oracle(cfg, world, rank, res)
+    else:
+        res["check_oracle"] = "not run for this configuration (its layer shape is checked against the oracle by the test-suite)"
+    flag = torch.tensor([float(len(problems))], device="cuda")
+    if world > 1:
+        dist.all_reduce(flag)
+    res["check"] = "ok" if float(flag) == 0 else "FAILED: " + "; ".join(problems or ["see another rank"])
+    return res
 
-    # two layers of the benchmark's layer shape, sharded like the benchmark, against the CPU oracle
-    c = dict(vocab=2048, max_pos=128, hidden=CFG["hidden"], heads=CFG["heads"], ffn=CFG["ffn"], depth=2, B=CFG["batch"], S=32, new=5)
+
+def verify_against_oracle(cfg, world, rank, res):
+    """Two layers of the benchmark's layer shape, sharded like the benchmark, prompt pass + a few
+    replayed generation steps, against the CPU oracle (greedy tokens; a divergence is excused only
+    where the oracle's own fp32 top-2 margin is below the activation tolerance)."""
+    import torch
+    from energonai_b200.gemm import device_status
     from energonai_b200.model import PipelineModel
+    from energonai_b200.sharding import shard_model_state
+    from oracle import inputs, layers      # the checker (never on the timed path)
+    problems = []
+    c = dict(vocab=2048, max_pos=128, hidden=cfg["hidden"], heads=cfg["heads"], ffn=cfg["ffn"], depth=2, B=cfg["batch"], S=32, new=5)
+    dt = torch_dtype(cfg)
     p = inputs.model_params(3, c["vocab"], c["max_pos"], c["hidden"], c["ffn"], c["depth"], rich=True)
     ids, mask, _ = inputs.left_padded_prompts(3, c["B"], c["S"], c["S"] // 2, c["S"], c["vocab"])
     tgt = c["S"] + c["new"]
-    full = {k: v.half() for k, v in layers.model_to_reference_state(p, c["depth"], False).items()}
+    full = {k: v.to(dt) for k, v in layers.model_to_reference_state(p, c["depth"], cfg["fused_qkv"]).items()}
     with torch.device("cuda"):
         small = PipelineModel(vocab_size=c["vocab"], max_seq_len=c["max_pos"], hidden_size=c["hidden"], num_heads=c["heads"],
-                              depth=c["depth"], mlp_ratio=c["ffn"] / c["hidden"], activation=torch.nn.functional.relu,
-                              dtype=torch.float16, fused_qkv=False, vocab_parallel=world > 1).eval()
+                              depth=c["depth"], mlp_ratio=c["ffn"] / c["hidden"], activation=activation_of(cfg), dtype=dt,
+                              fused_qkv=cfg["fused_qkv"], vocab_parallel=world > 1).eval()
     small.load_state_dict(shard_model_state(full, rank, world, vocab_parallel=world > 1), strict=True)
     del full
     got = small(input_ids=ids.cuda(), attention_mask=mask.cuda(), max_tokens=tgt, top_k=1)      # replayed steps
@@ -338,7 +437,7 @@ def verify(world, rank, out_tokens):
     if rank == 0:
         rec = {}
         with torch.inference_mode():
-            want = layers.OracleModel(p, c["depth"], c["heads"], "relu").generate(ids, mask, tgt, rec)
+            want = layers.OracleModel(p, c["depth"], c["heads"], cfg["act"]).generate(ids, mask, tgt, rec)
         logits = torch.stack(rec["logits"], 0)
         top2 = logits.topk(2, -1).values
         margin = (top2[..., 0] - top2[..., 1])              # [new, B]
@@ -356,95 +455,117 @@ def verify(world, rank, out_tokens):
         problems.append(f"device status after the check run: {st}")
     del small
     torch.cuda.empty_cache()
-    flag = torch.tensor([float(len(problems))], device="cuda")
-    if world > 1:
-        dist.all_reduce(flag)
-    res["check"] = "ok" if float(flag) == 0 else "FAILED: " + "; ".join(problems or ["see another rank"])
-    return res
+    return problems
 
 
-def run_ours(args):
+def init_group(cfg, bulk_rows):
+    """Process group + tensor-parallel context.  Returns (world, rank, local, exchange description)."""
     import torch
     import torch.distributed as dist
     from energonai_b200 import tp
-    from oracle import inputs   # seeded prompt generator only (no oracle compute on the timed path)
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    cfg = dict(CFG)
-    if args.layers:
-        cfg["depth"] = args.layers
-    if args.new_tokens:
-        cfg["new_tokens"] = args.new_tokens
-    exchange_kind = "none (one rank)"
+    kind = "none (one rank)"
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         ctx = tp.init_tp(world)
-        exchange_kind = "NCCL all-reduce"
+        kind = "NCCL all-reduce"
         if os.environ.get("EB_PEER", "1") != "0":
-            # generation steps: the all-reduces run inside the library's own kernels over NVLink peer memory
+            # the all-reduces run inside the library's own kernels over NVLink peer memory
             try:
-                bulk = cfg["batch"] * cfg["prompt"] if os.environ.get("EB_PEER_PROMPT", "1") != "0" else 0
+                bulk = bulk_rows if os.environ.get("EB_PEER_PROMPT", "1") != "0" else 0
                 ctx.enable_peer_exchange(128, cfg["hidden"], bulk_rows=bulk)
-                exchange_kind = ("prompt pass: " + ("reduce-scatter in the GEMM epilogue + reduce/broadcast kernel, NVLink peer stores"
-                                                    if bulk else "NCCL all-reduce") +
-                                 "; generation steps: inside the chained kernel, NVLink peer stores")
+                kind = ("prompt pass: " + ("reduce-scatter in the GEMM epilogue + reduce/broadcast kernel, NVLink peer stores"
+                                          if bulk else "NCCL all-reduce") +
+                        "; generation steps: in the epilogue of the row-parallel GEMMs, NVLink peer stores")
             except Exception as e:          # no peer mapping on this box: NCCL carries every all-reduce
                 ctx.peer = None
                 if rank == 0:
                     print(f"peer exchange unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
-    model = build_model(cfg, torch.float16, world)
-    ids_h, mask_h, _ = inputs.left_padded_prompts(0, cfg["batch"], cfg["prompt"], cfg["len_lo"], cfg["prompt"], cfg["vocab"])
-    ids_h, mask_h = ids_h.pin_memory(), mask_h.pin_memory()
-    ids_d, mask_d = ids_h.cuda(), mask_h.cuda()
-    tgt = cfg["prompt"] + cfg["new_tokens"]
-    tokens_per_step = cfg["batch"] * tgt
+    return world, rank, local, kind
+
+
+def finish(world, model=None):
+    # Captured graphs hold NCCL kernels; tearing the process group down under them can block,
+    # so release the graphs, rendezvous once more and leave without the teardown.
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        if model is not None:
+            model._decode_state = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
+def run_generation(args, cfg):
+    import torch
+    import torch.distributed as dist
+    cfg = dict(cfg)
+    if args.layers:
+        cfg["depth"] = args.layers
+    if args.new_tokens:
+        cfg["new_tokens"] = args.new_tokens
+    batches_h = make_batches(cfg)
+    world, rank, local, exchange_kind = init_group(cfg, max(i.shape[0] * i.shape[1] for i, _, _ in batches_h))
+    model = build_model(cfg, world)
+    batches_d = [(i.cuda(), m.cuda(), t) for i, m, t in batches_h]
+    new_total = sum(i.shape[0] for i, _, _ in batches_h) * cfg["new_tokens"]
+    tokens_per_step = sum(i.shape[0] * t for i, _, t in batches_h)
+    bucketed = "requests" in cfg
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def one(resident, rec=None):
+    def one(k, resident, rec=None):
         if resident:
-            return model(input_ids=ids_d, attention_mask=mask_d, max_tokens=tgt, top_k=1, record=rec)
-        out = model(input_ids=ids_h.cuda(non_blocking=True), attention_mask=mask_h.cuda(non_blocking=True),
-                    max_tokens=tgt, top_k=1)
+            ids, mask, tgt = batches_d[k]
+            return model(input_ids=ids, attention_mask=mask, max_tokens=tgt, top_k=1, record=rec)
+        ids, mask, tgt = batches_h[k]
+        out = model(input_ids=ids.cuda(non_blocking=True), attention_mask=mask.cuda(non_blocking=True), max_tokens=tgt, top_k=1)
         return out.cpu()
 
-    for _ in range(args.warmup):
-        one(True)
     sampler = ClockSampler(local)
-    barrier()
-    if rank == 0:
-        sampler.start()
-    recs, launches = [], 0
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        rec = {"allow_graph": True}
-        out = one(True, rec)
-        recs.append(rec)
-        launches += model.launches_last_call
-    ev1.record()
-    barrier()
+    elapsed_ms = e2e_ms = 0.0
+    recs, launches, outs = [], 0, []
+    # A batch shape owns its caches and its captured step: batches are measured one after the
+    # other (warm-up, device-resident arm, host-to-host arm), and the times are added up.
+    for k in range(len(batches_d)):
+        for _ in range(args.warmup):
+            one(k, True)
+        barrier()
+        if rank == 0 and k == 0:
+            sampler.start()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(args.steps):
+            rec = {"allow_graph": True}
+            out = one(k, True, rec)
+            rec["batch"] = batches_d[k][0].shape[0]
+            recs.append(rec)
+            launches += model.launches_last_call
+        ev1.record()
+        barrier()
+        elapsed_ms += ev0.elapsed_time(ev1)
+        outs.append(out)
+        assert out.shape == (batches_d[k][0].shape[0], batches_d[k][2]), out.shape
+        # the same metric end to end: host (pinned) inputs in, host tokens out, copies inside the timed region
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            out_h = one(k, False)
+        e1.record()
+        barrier()
+        e2e_ms += e0.elapsed_time(e1)          # device time; the .cpu() read of the tokens is synchronous
     clocks = sampler.stop() if rank == 0 else None
-    elapsed_ms = ev0.elapsed_time(ev1)
-    assert out.shape == (cfg["batch"], tgt), out.shape
-
-    # the same metric end to end: host (pinned) inputs in, host tokens out, copies inside the timed region
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        out_h = one(False)
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)          # device time; the .cpu() read of the tokens is synchronous
-
     if world > 1:
         t = torch.tensor([elapsed_ms, e2e_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -456,74 +577,268 @@ def run_ours(args):
         ev = rec["step_events"]
         prefill_ms.append(ev[0].elapsed_time(ev[1]))
         step_ms += [a.elapsed_time(b) for a, b in zip(ev[1:-1], ev[2:])]
-    prefill_mean = statistics.mean(prefill_ms)
+    prefill_sum = sum(prefill_ms) / args.steps                      # all batches of one job
     step_p50 = statistics.median(step_ms) if step_ms else None
+    step_p99 = sorted(step_ms)[min(len(step_ms) - 1, int(0.99 * len(step_ms)))] if step_ms else None
     peaks = measured_peaks()
 
-    # ---- explanations, outside the timed region ----
-    probe = probe_decode_kernels(model, cfg, model._decode_state, world)
-    exposed = exposed_exchange(model, cfg, ids_d, mask_d, tgt, prefill_mean, step_p50) if world > 1 else None
-    checks = verify(world, rank, out) if not args.no_check else {"check": "skipped"}
-
-    def finish():
-        # Captured graphs hold NCCL kernels; tearing the process group down under them can
-        # block, so release the graphs, rendezvous once more and leave without the teardown.
-        if world > 1:
-            model._decode_state = None
-            torch.cuda.synchronize()
-            dist.barrier()
-            sys.stdout.flush()
-            sys.stderr.flush()
-            os._exit(0)
-
+    # ---- explanations, outside the timed region (on the last batch shape, whose step is captured) ----
+    last_B = batches_d[-1][0].shape[0]
+    probe = probe_decode_kernels(model, cfg, model._decode_state, world, last_B)
+    exposed = None
+    if world > 1 and not bucketed:
+        ids, mask, tgt = batches_d[0]
+        exposed = exposed_exchange(model, ids, mask, tgt, prefill_ms[-1], step_p50)
+    if args.no_check:
+        checks = {"check": "skipped"}
+    else:
+        checks = verify(cfg, world, rank, torch.cat([o.reshape(-1) for o in outs]), with_oracle=args.config == 3)
     if rank != 0:
-        finish()
+        finish(world, model)
         return
     achieved = probe["bytes"] / (probe["ms"] * 1e-3) / 1e9
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "decode_gemm_dram_bytes_per_launch.txt")
-    if world == 1 and not args.layers and os.path.exists(tpath):
+    if world == 1 and args.config == 3 and not args.layers and os.path.exists(tpath):
         with open(tpath) as f:            # dram__bytes_read.sum + dram__bytes_write.sum per launch, from an ncu capture
             traffic = float(f.read().split()[0])
     roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s", "frac": achieved / peaks["hbm"],
             "traffic": traffic, "kernel": probe["kernel"], "peak_kind": f"of {peaks['kind']}",
             "launches_timed": probe["launches"], "algorithmic_bytes_per_launch": probe["bytes"] / max(1, probe["launches"]),
             "us_per_launch": probe["ms"] * 1e3 / max(1, probe["launches"])}
-    if step_p50:
+    h, f = cfg["hidden"], cfg["ffn"]
+    if step_p50 and not bucketed:
         kv_mid = cfg["prompt"] + cfg["new_tokens"] // 2
-        whole = step_bytes(cfg, world, kv_mid) / (step_p50 * 1e-3) / 1e9
-        roof["whole_step"] = {"algorithmic_bytes_per_rank": step_bytes(cfg, world, kv_mid), "achieved": whole, "frac": whole / peaks["hbm"],
+        sb = step_bytes(cfg, world, cfg["batch"], kv_mid)
+        roof["whole_step"] = {"algorithmic_bytes_per_rank": sb, "achieved": sb / (step_p50 * 1e-3) / 1e9,
+                              "frac": sb / (step_p50 * 1e-3) / 1e9 / peaks["hbm"],
                               "note": "weights + keys/values + LM head of one rank / decode_step_ms_p50"}
-    h, f, T = cfg["hidden"], cfg["ffn"], cfg["batch"] * cfg["prompt"]
-    prompt_flops = cfg["depth"] * (2 * T * h * (4 * h + 2 * f) + 4 * cfg["batch"] * cfg["prompt"] ** 2 * h / 2) / world
-    roof["prompt_pass"] = {"bound": "tensor", "achieved": prompt_flops / (prefill_mean * 1e-3) / 1e12, "unit": "TFLOP/s",
-                           "peak": peaks["tensor_sustained"], "frac": prompt_flops / (prefill_mean * 1e-3) / 1e12 / peaks["tensor_sustained"],
+    prompt_flops = sum(cfg["depth"] * (2 * i.shape[0] * i.shape[1] * h * (4 * h + 2 * f) + 4 * i.shape[0] * i.shape[1] ** 2 * h / 2)
+                       for i, _, _ in batches_h) / world
+    roof["prompt_pass"] = {"bound": "tensor", "achieved": prompt_flops / (prefill_sum * 1e-3) / 1e12, "unit": "TFLOP/s",
+                           "peak": peaks["tensor_sustained"],
+                           "frac": prompt_flops / (prefill_sum * 1e-3) / 1e12 / peaks["tensor_sustained"],
                            "note": "GEMM + causal-useful attention flops of one rank / prefill_ms, against the sustained bf16 GEMM peak"}
     ms_per_step = elapsed_ms / args.steps
-    value = tokens_per_step / (ms_per_step * 1e-3)
-    config = workload_config(world)
+    config = workload_config(cfg, world)
     config["exchange"] = exchange_kind
     config["lm_head"] = "vocabulary split over the ranks" if world > 1 else "replicated"
-    line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+    if bucketed:
+        config["buckets"] = [{"padded_len": int(i.shape[1]), "requests": int(i.shape[0])} for i, _, _ in batches_h]
+        value = new_total / (ms_per_step * 1e-3 - prefill_sum * 1e-3) if ms_per_step > prefill_sum else None
+        value_note = "generated tokens / time of the generation steps of all buckets (prompt passes reported beside it)"
+    else:
+        value = tokens_per_step / (ms_per_step * 1e-3)
+        value_note = "(prompt + generated tokens) / time of the whole job"
+    n_prompt_tok = sum(i.shape[0] * i.shape[1] for i, _, _ in batches_h)
+    line = {"metric": cfg["metric"], "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "fp16", "data": "synthetic", "config": config,
-            "prefill_tokens_per_s": cfg["batch"] * cfg["prompt"] / (prefill_mean * 1e-3),
-            "decode_tokens_per_s": cfg["batch"] / (statistics.mean(step_ms) * 1e-3) if step_ms else None,
-            "decode_step_ms_p50": step_p50, "prefill_ms": prefill_mean,
-            "e2e": {"value": tokens_per_step / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": ids_h.numel() * ids_h.element_size() + mask_h.numel() * mask_h.element_size(),
-                    "d2h_bytes_per_step": out_h.numel() * out_h.element_size()},
+            "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic", "config": config, "value_is": value_note,
+            "prefill_tokens_per_s": n_prompt_tok / (prefill_sum * 1e-3),
+            "decode_tokens_per_s": new_total / (sum(step_ms) / args.steps * 1e-3) if step_ms else None,
+            "decode_step_ms_p50": step_p50, "decode_step_ms_p99": step_p99, "prefill_ms": prefill_sum,
+            "e2e": {"value": (tokens_per_step if not bucketed else new_total) / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": sum(i.numel() * i.element_size() + m.numel() * m.element_size() for i, m, _ in batches_h),
+                    "d2h_bytes_per_step": sum(o.numel() * o.element_size() for o in outs)},
             "gpu_launches": launches, "clocks": clocks, "roofline": roof}
+    if bucketed:
+        line["e2e"]["note"] = "whole jobs (prompt passes included) with host inputs and outputs; tokens counted = generated tokens"
     line.update(checks)
     if exposed:
         line.update(exposed)
-    if world == 1 and not args.no_cpu:
-        v, sample, cores, _ = cpu_sample(CFG)
+    if world == 1 and not args.no_cpu and not bucketed:
+        v, sample, cores, _ = cpu_sample(CONFIGS[args.config])
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
     if args.layers or args.new_tokens:
         line["config"]["reduced"] = f"depth {cfg['depth']}, new_tokens {cfg['new_tokens']} (debug run, not the named config)"
     print(json.dumps(line), flush=True)
-    finish()
+    finish(world, model)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU arm: the encoder block on the kernel API (configuration 2)
+# ------------------------------------------------------------------------------------------------
+class PackedEncoderBlock:
+    """A post-LN encoder block (the reference's BERT example, examples/bert/bert.py:66-187) that
+    works on the PACKED tokens of a right-padded batch, through the kernel API the reference
+    exposes for that purpose: ft_build_padding_offsets + ft_remove_padding before the block,
+    ft_transpose_rebuild_padding / ft_transpose_remove_padding around the attention product,
+    scale_mask_softmax (key-length mask, scale 1/sqrt(d)) on the score tensor, LayerNorm with the
+    residual fused, ft_rebuild_padding after the block; linear layers on the tcgen05 GEMM; the
+    two batched products QK^T and PV through torch.matmul, as in the reference."""
+
+    def __init__(self, bp, heads, dtype, rank=0, world=1):
+        import torch
+        dev = "cuda"
+        self.H, self.world, self.rank = heads // world, world, rank
+        h = bp["q.weight"].shape[1]
+        self.h, self.d = h, h // heads
+        hl = h // world
+
+        def rows(w):
+            return w[rank * (w.shape[0] // world):(rank + 1) * (w.shape[0] // world)]
+
+        def cols(w):
+            return w[:, rank * (w.shape[1] // world):(rank + 1) * (w.shape[1] // world)]
+        t = lambda v: v.to(dtype).to(dev).contiguous()
+        self.wqkv = t(torch.cat([rows(bp["q.weight"]), rows(bp["k.weight"]), rows(bp["v.weight"])], 0))
+        self.bqkv = t(torch.cat([rows(bp["q.bias"]), rows(bp["k.bias"]), rows(bp["v.bias"])], 0))
+        self.wo, self.bo = t(cols(bp["dense.weight"])), t(bp["dense.bias"])
+        self.w1, self.b1 = t(rows(bp["fc1.weight"])), t(rows(bp["fc1.bias"]))
+        self.w2, self.b2 = t(cols(bp["fc2.weight"])), t(bp["fc2.bias"])
+        self.g1, self.be1, self.g2, self.be2 = t(bp["norm1.weight"]), t(bp["norm1.bias"]), t(bp["norm2.weight"]), t(bp["norm2.bias"])
+        self.hl = hl
+
+    def forward(self, x, lens, B, S):
+        """x [B, S, h] (rows beyond lens[b] ignored), lens int32 [B] on the device.  Returns [B, S, h]
+        with zero rows at the padding."""
+        import torch
+        from energonai_b200 import kernel as EK
+        from energonai_b200 import tp
+        from energonai_b200._lib import SM_ALLROWS, SM_KEYLEN
+        from energonai_b200.gemm import gemm
+        from energonai_b200.kernel.cuda_native.layer_norm import layer_norm_forward
+        h, H, d, hl = self.h, self.H, self.d, self.hl
+        valid = torch.zeros(1, dtype=torch.int32, device=x.device)
+        tmp = torch.empty(B * S, dtype=torch.int32, device=x.device)
+        off = torch.empty(B * S, dtype=torch.int32, device=x.device)
+        EK.ft_build_padding_offsets(lens, B, S, valid, tmp)
+        V = self.valid_tokens                  # known on the host (a .item() here would stall the stream)
+        packed = EK.ft_remove_padding(x, tmp, off, V, h).view(V, h)
+        # post-LN block (endecoder.py:52-69 with apply_post_layernorm): norm first, residual = the normed row
+        n1 = layer_norm_forward(packed, self.g1, self.be1, 1e-5)
+        qkv = gemm(n1, self.wqkv, bias=self.bqkv, static_weight=True)                     # [V, 3*hl]
+        q, k, v = (torch.zeros(B, H, S, d, dtype=x.dtype, device=x.device) for _ in range(3))
+        EK.ft_transpose_rebuild_padding(qkv[:, :hl].contiguous().view(1, V, H, d), qkv[:, hl:2 * hl].contiguous().view(1, V, H, d),
+                                        qkv[:, 2 * hl:].contiguous().view(1, V, H, d), q, k, v, B, S, H, d, V, off)
+        scores = torch.matmul(q, k.transpose(-1, -2))                                     # [B, H, S, S]
+        EK.scale_mask_softmax(B, S, H, scores, lens, flags=SM_KEYLEN | SM_ALLROWS, scale=d ** -0.5)
+        ctx = torch.matmul(scores, v)                                                     # [B, H, S, d]
+        ctx = EK.ft_transpose_remove_padding(ctx, V, B, S, H, d, off).view(V, hl)
+        lead = self.rank == 0
+        a = gemm(ctx, self.wo, bias=self.bo if lead else None, residual=n1 if lead else None, static_weight=True)
+        tp.get_tp().all_reduce(a)
+        n2 = layer_norm_forward(a, self.g2, self.be2, 1e-5)
+        inter = gemm(n2, self.w1, bias=self.b1, act="gelu", static_weight=True)
+        y = gemm(inter, self.w2, bias=self.b2 if lead else None, residual=n2 if lead else None, static_weight=True)
+        tp.get_tp().all_reduce(y)
+        return EK.ft_rebuild_padding(y.view(1, V, h), off, V, h, B, S)
+
+
+def run_encoder_block(args, cfg):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from energonai_b200 import _lib
+    from oracle import inputs, layers
+    world, rank, local, exchange_kind = init_group(cfg, 0)
+    dt = torch_dtype(cfg)
+    B, S, h, H, f = cfg["batch"], cfg["seq"], cfg["hidden"], cfg["heads"], cfg["ffn"]
+    gen = torch.Generator().manual_seed(1)
+    bp = inputs.block_params(gen, h, f)
+    lens_h = inputs.right_padded_lengths(1, B, cfg["len_lo"], S)
+    V = int(lens_h.sum())
+    valid = torch.arange(S)[None, :] < lens_h[:, None]
+    xs_h = [(torch.randn(B, S, h, generator=gen) * valid[:, :, None]).to(dt).pin_memory() for _ in range(8)]
+    xs = [x.cuda() for x in xs_h]
+    lens = lens_h.cuda()
+    blk = PackedEncoderBlock(bp, H, dt, rank, world)
+    blk.valid_tokens = V
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(3, args.warmup)):
+        out = blk.forward(xs[i % 8], lens, B, S)
+    passes = 16                                                   # passes of the block per timed step
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    l0 = _lib.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for s_ in range(args.steps):
+        for i in range(passes):
+            out = blk.forward(xs[i % 8], lens, B, S)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = _lib.launch_count - l0
+    ms = ev0.elapsed_time(ev1) / args.steps
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for s_ in range(args.steps):
+        for i in range(passes):
+            out_h = blk.forward(xs_h[i % 8].cuda(non_blocking=True), lens, B, S).cpu()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+
+    # ---- the dominant memory-bound kernel of this workload timed alone: scale_mask_softmax ----
+    from energonai_b200 import kernel as EK
+    from energonai_b200._lib import SM_ALLROWS, SM_KEYLEN
+    Hl = H // world
+    bufs = [torch.randn(B, Hl, S, S, device="cuda", dtype=dt) for _ in range(max(2, 8 // world))]
+    for b in bufs[:2]:
+        EK.scale_mask_softmax(B, S, Hl, b, lens, flags=SM_KEYLEN | SM_ALLROWS, scale=0.125)
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for b in bufs:
+        EK.scale_mask_softmax(B, S, Hl, b, lens, flags=SM_KEYLEN | SM_ALLROWS, scale=0.125)
+    k1.record()
+    torch.cuda.synchronize()
+    sm_us = k0.elapsed_time(k1) * 1e3 / len(bufs)
+    sm_bytes = (V + B * S) * S * Hl * 2                           # visible keys read + every row written
+    peaks = measured_peaks()
+
+    # ---- parity of what was timed, outside the timed region ----
+    problems = []
+    if rank == 0 or world > 1:
+        x0 = xs_h[0].float()
+        m4 = (1.0 - valid.float().view(B, 1, 1, S)) * -10000.0
+        got = blk.forward(xs[0], lens, B, S).float().cpu()
+        if rank == 0:
+            with torch.inference_mode():
+                bp_r = {k: v.to(dt).float() for k, v in bp.items()}
+                want = layers.OracleBlock(bp_r, H, "gelu", apply_post_layernorm=True, is_decoder=False)(x0, m4, True)
+            err = (got - want).abs()[valid]
+            if not bool((err <= 2e-2 + 1e-2 * want.abs()[valid]).all()):
+                problems.append(f"block output differs from the oracle (max err {float(err.max()):.3g})")
+            if bool(got[~valid].any()):
+                problems.append("padding rows are not zero")
+    from energonai_b200.gemm import device_status
+    if device_status()[0] != 0:
+        problems.append("device status not clear")
+    if rank != 0:
+        finish(world)
+        return
+    tokens = V * passes
+    line = {"metric": cfg["metric"], "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": cfg["dtype"], "data": "synthetic", "config": dict(workload_config(cfg, world), exchange=exchange_kind,
+                                                                       valid_tokens=V, passes_per_step=passes),
+            "block_ms": ms / passes,
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": passes * xs_h[0].numel() * xs_h[0].element_size(),
+                    "d2h_bytes_per_step": passes * out_h.numel() * out_h.element_size()},
+            "gpu_launches": launches, "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "softmax_kernel (scale_mask_softmax, key-length mask, all rows)",
+                         "achieved": sm_bytes / sm_us / 1e3, "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": sm_bytes / sm_us / 1e3 / peaks["hbm"], "traffic": None, "peak_kind": f"of {peaks['kind']}",
+                         "us_per_launch": sm_us, "algorithmic_bytes_per_launch": sm_bytes},
+            "check": "ok" if not problems else "FAILED: " + "; ".join(problems)}
+    print(json.dumps(line), flush=True)
+    finish(world)
 
 
 def main():
@@ -532,6 +847,9 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=3, choices=sorted(CONFIGS),
+                    help="BASELINE configuration: 3 = OPT-13B generation (the headline, default), 4 = GPT-3 slab, "
+                         "5 = OPT-66B bucketed decode, 2 = BERT-large block on the kernel API")
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers (marks the line as reduced)")
     ap.add_argument("--new-tokens", type=int, default=0, help="debug: fewer generation steps (marks the line as reduced)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -539,8 +857,10 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif CONFIGS[args.config]["kind"] == "generation":
+        run_generation(args, CONFIGS[args.config])
     else:
-        run_ours(args)
+        run_encoder_block(args, CONFIGS[args.config])
 
 
 if __name__ == "__main__":

@@ -155,7 +155,7 @@ extern "C" int eb_comm_create(int rank, int world, size_t line_bytes, size_t bul
   if (!c) return fail(EB_ECUDA, "comm_create: out of host memory");
   c->rank = rank; c->world = world; c->device = dev; c->recv_bytes = recv_bytes;
   c->line_bytes = line_bytes; c->bulk_bytes = bulk_bytes;
-  c->wait_budget_ns = 1000ull * 1000ull * 1000ull;
+  c->wait_budget_ns = 5ull * 1000ull * 1000ull * 1000ull;     // 5 s: ranks may be seconds apart while one of them loads code or captures a graph
   cudaError_t e = cudaSuccess;
   if (recv_local) {
     c->recv[rank] = recv_local;

@@ -70,7 +70,7 @@ struct GemmParams {
   int stages;                    // pipeline depth actually used (<= kMaxStages)
   int kpb;                       // k-blocks (64 columns each) per pipeline stage / barrier hand-over
   int static_w;                  // W may be read before the preceding kernel of the stream has finished
-  // Fused all-reduce of the generation orientation (comm.world > 1): the CTA that completes a
+  // Fused all-reduce of the generation orientation (comm.world >= 1; a single rank exchanges with itself): the CTA that completes a
   // tile sends this rank's partial product to every rank as flagged lines and adds up what the
   // ranks sent it (see comm.cuh).  A thread's BN batch values of output column n are contiguous
   // in the receive area: lines [source][n][BN / 4].
@@ -81,6 +81,11 @@ struct GemmParams {
   int rs;
   long long rs_rpr;
   unsigned long long rs_stage_off;
+  // Optional: once this launch has requested all its own tiles, its producer warps ask for
+  // [pf_ptr, pf_ptr + pf_bytes) to be brought into L2: the weights of the launch that follows,
+  // which then streams them from L2 while this launch is still in its epilogue.
+  const unsigned char *pf_ptr;
+  unsigned long long pf_bytes;
   // swap mode, optional: the A operand is the un-normalised input of a LayerNorm whose scale
   // was multiplied into W beforehand.  The kernel computes each row's mean / inverse std over
   // K itself and the last epilogue of a tile evaluates
@@ -163,6 +168,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 // Asks for a weight tile to be brought into L2 (no shared-memory destination, no completion).
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
+// Asks for `bytes` (a multiple of 16) at a 16-byte aligned address to be brought into L2.
+__device__ __forceinline__ void prefetch_l2_bulk(const void *ptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -430,6 +439,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
       }
     }
     }   // mover lanes
+    // The following launch's weights: 8 KB pieces dealt round-robin over the CTAs and the lanes.
+    if (p.pf_bytes) {
+      constexpr unsigned long long kPiece = 8192;
+      const unsigned long long pieces = (p.pf_bytes + kPiece - 1) / kPiece;
+      for (unsigned long long i = (unsigned long long)blockIdx.x * 32 + lane; i < pieces; i += (unsigned long long)gridDim.x * 32) {
+        const unsigned long long off = i * kPiece;
+        const unsigned long long left = p.pf_bytes - off;
+        prefetch_l2_bulk(p.pf_ptr + off, (uint32_t)(left < kPiece ? left & ~15ull : kPiece));
+      }
+    }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     griddep_wait();
@@ -471,7 +490,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
     const T *bias = reinterpret_cast<const T *>(p.bias);
     const T *res = reinterpret_cast<const T *>(p.residual);
     // sequence number of this launch's exchange (the counter is advanced when the grid is done)
-    const uint32_t comm_seq = (SWAP && p.comm.world > 1) ? *reinterpret_cast<volatile unsigned int *>(p.comm.ctl + kCtlEpoch) + 1u : 0u;
+    const uint32_t comm_seq = (SWAP && p.comm.world >= 1) ? *reinterpret_cast<volatile unsigned int *>(p.comm.ctl + kCtlEpoch) + 1u : 0u;
     Scheduler<BN, SWAP> sched(p);
     Segment s;
     int acc = 0;
@@ -479,11 +498,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
     bool alive = true;
     // Rendezvous of the 128 epilogue threads with a bounded wait (a plain bar.sync could not
     // be abandoned if one warp had already left on an abort).
+    // (Every give-up is made uniform over the warp with a vote before anybody acts on it: a
+    // lane that left while the others went on to a warp-synchronous instruction, a shuffle or a
+    // tensor-memory load, would leave them waiting for it for ever.)
     auto epi_sync = [&]() {
       mbar_arrive(epi_bar);
       const bool ok = mbar_wait(epi_bar, epi_phase, abort_flag, 5);
       epi_phase ^= 1u;
-      return ok;
+      return __all_sync(0xffffffffu, ok) != 0;
     };
     // Folded LayerNorm: row statistics of the activations, computed here while the first
     // weight stages are on their way (these warps have nothing else to do yet).  BN / 128 of
@@ -557,7 +579,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
         first_cta = t0 / p.units_per_cta;
         last_cta = (t0 + sched.nsk - 1) / p.units_per_cta;
       }
-      if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, 4))) break;
       tcgen05_fence_after();
       const uint32_t t_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
 
@@ -772,7 +794,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
             }
           }
         }
-        if (do_epilogue && p.comm.world > 1 && n_ok) {
+        bool lost = false;
+        if (do_epilogue && p.comm.world >= 1 && n_ok) {
           // Fused all-reduce: this thread holds the rank's complete partial products of output
           // column n for every batch row.  They go to every rank (this one included) as flagged
           // lines, rounded to the operand type (what an all-reduce of the product would carry);
@@ -806,7 +829,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           // Collect: the lines of kSrc sources at a time are requested together and their
           // sequence numbers looked at afterwards (a test between two loads would serialise them).
           constexpr int kSrc = kLines <= 4 ? 4 : (kLines <= 8 ? 2 : 1);
-          bool lost = false;
           for (int r0 = 0; r0 < cm.world && !lost; r0 += kSrc) {
             LlLine got[kSrc][kLines];
             const unsigned char *src = cm.recv[cm.rank] + half + ((unsigned long long)r0 * per_src + (unsigned long long)n * kLines) * 16ull;
@@ -848,8 +870,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
                 }
               }
           }
-          if (lost) { alive = false; continue; }
         }
+        // a peer's lines never came: the whole warp leaves together (lanes without a column of
+        // their own, beyond N, did not wait and must not be left behind at the next tile)
+        if (p.comm.world >= 1 && __any_sync(0xffffffffu, lost)) { alive = false; continue; }
         if (do_epilogue && n_ok && row_ok) {
           // offset of row m of C, advanced row by row (a division per row by the run-time
           // rows-per-batch cost 0.1 us each: 2 us per tile)
@@ -928,7 +952,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
   // ---------------- teardown ----------------
   tcgen05_fence_before();
   __syncthreads();
-  if (SWAP && p.comm.world > 1 && threadIdx.x == 0) {
+  if (SWAP && p.comm.world >= 1 && threadIdx.x == 0) {
     // the last CTA of the grid advances the exchange's sequence number for the next launch
     unsigned int *ctl = p.comm.ctl;
     const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(ctl + kCtlEpoch) + 1u;
@@ -1046,11 +1070,12 @@ int launch_chain(const ChainMaps &maps, const ChainParams &p, int grid, size_t s
   return check_launch("decode_chain");
 }
 
-// Workspace of a chain: [4 KB arrival counters of the operations][kMaxOps x 16 KB tile counters]
-// [stream-K partial sums of the GEMMs, one area each].  Every counter sits at an offset that
+// Workspace of a chain: [4 KB: arrival counters of the operations, then at byte 512 the per-row
+// counters of the reductions][kMaxOps x 16 KB tile counters][per operation, in order: the
+// stream-K partial sums of a GEMM, or the slice statistics of a reduction].  Every counter sits at an offset that
 // does not depend on the operations, so chains of different make-up can share one zero-filled
 // workspace: no chain's partial sums ever land on another chain's counters.
-constexpr size_t kChainHeadBytes = 4096, kChainTileCounterBytes = 16384;
+constexpr size_t kChainHeadBytes = 4096, kChainTileCounterBytes = 16384, kChainStatsBytes = 8192;
 constexpr size_t kChainPartialOffset = kChainHeadBytes + kMaxOps * kChainTileCounterBytes;
 
 inline size_t chain_op_bytes(int grid, int bn) { return (size_t)grid * 2 * bn * kLanes * sizeof(float); }
@@ -1063,8 +1088,10 @@ using namespace eb;
 extern "C" size_t eb_decode_chain_workspace_bytes(const eb_chain_op *ops, int n_ops, int M) {
   if (!ops || n_ops <= 0 || n_ops > kMaxOps || M <= 0 || M > kLanes) return 0;
   size_t total = kChainPartialOffset;
-  for (int i = 0; i < n_ops; ++i)
+  for (int i = 0; i < n_ops; ++i) {
     if (ops[i].type == EB_OP_GEMM) total += chain_op_bytes(sm_count(), swap_bn(M));
+    if (ops[i].type == EB_OP_REDUCE_LAYERNORM) total += kChainStatsBytes;
+  }
   return total;
 }
 
@@ -1162,6 +1189,12 @@ extern "C" int eb_decode_chain(const eb_chain_op *ops, int n_ops, int M, int dty
       l.gamma = o.gamma; l.beta = o.beta; l.y = o.y; l.n2 = o.n2; l.eps = (float)o.eps;
       l.bias = o.bias; l.residual = o.residual; l.ldr = o.ldr; l.sum_out = o.C; l.ld_sum = o.ldc;
       l.exchange = pending_exchange;
+      // column slices per row: as many CTAs as the grid spares, at most eight
+      l.split = grid / M >= 8 ? 8 : grid / M >= 4 ? 4 : grid / M >= 2 ? 2 : 1;
+      l.rowdone = reinterpret_cast<int *>(reinterpret_cast<char *>(workspace) + 512) + pending_exchange * kLanes;
+      l.stats = reinterpret_cast<float2 *>(cursor);          // [128 rows][8 slices], needs no initialisation
+      cursor += kChainStatsBytes;
+      EB_REQUIRE(pending_exchange < 7, "decode_chain: too many exchanges in one chain");
       pending_exchange = -1;
     } else {
       return fail(EB_EINVAL, "decode_chain: op %d: unknown type %d", i, o.type);
@@ -1203,6 +1236,18 @@ extern "C" int eb_device_status(int *out4, int clear) {
     int zero[4] = {0, 0, 0, 0};
     cudaMemcpyToSymbol(g_status, zero, sizeof(zero));
   }
+  return EB_OK;
+}
+
+namespace {
+thread_local const void *t_prefetch_ptr = nullptr;
+thread_local size_t t_prefetch_bytes = 0;
+}  // namespace
+
+extern "C" int eb_gemm_prefetch_hint(const void *next_weights, size_t bytes) {
+  EB_REQUIRE(!next_weights || aligned16(next_weights), "gemm_prefetch_hint: the address must be 16-byte aligned");
+  t_prefetch_ptr = next_weights;
+  t_prefetch_bytes = next_weights ? bytes : 0;
   return EB_OK;
 }
 
@@ -1261,7 +1306,7 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
       return fail(EB_ELIMIT, "gemm_reduce_scatter: %d x %d from %d ranks needs %zu bytes of the bulk region at offset %zu, which has %zu",
                   M, N, comm->world, need, rs_stage_offset, comm->bulk_bytes);
     p.comm = comm_dev(comm);
-  } else if (comm && comm->world > 1) {
+  } else if (comm) {
     int dev = -1;
     cudaGetDevice(&dev);
     EB_REQUIRE(comm->connected && comm->device == dev, "gemm_allreduce: the context is not connected or belongs to another device");
@@ -1273,6 +1318,11 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
     p.comm = comm_dev(comm);
   }
   p.bias = bias; p.residual = residual; p.ldr = ldr; p.act = act; p.out_f32 = out_dtype == EB_F32 && dtype != EB_F32;
+  // a hint is consumed by the first launch after it, whatever that launch is
+  p.pf_ptr = reinterpret_cast<const unsigned char *>(t_prefetch_ptr);
+  p.pf_bytes = t_prefetch_bytes & ~(size_t)15;
+  t_prefetch_ptr = nullptr;
+  t_prefetch_bytes = 0;
 
   CUtensorMap tl, tc;
   int rc;

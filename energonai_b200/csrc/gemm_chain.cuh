@@ -52,6 +52,13 @@ struct ChainLn {
   void *sum_out;
   long long ld_sum;
   int exchange;
+  // kOpReduceLn: a row is cut into `split` column slices, one CTA each (CTA m * split + j takes
+  // slice j of row m), so that the collection of the ranks' lines is one or two rounds of loads
+  // per thread instead of ten; the slices' partial statistics meet in `stats` [row][slice] and
+  // `rowdone` [row] counts the slices that have delivered theirs (zero between launches).
+  int split;
+  float2 *stats;
+  int *rowdone;
 };
 
 struct ChainParams {

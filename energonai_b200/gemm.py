@@ -21,7 +21,7 @@ def workspace(device, nbytes):
 
 def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out_rows_per_batch=0,
          out_batch_stride=0, out_ld=None, out_row_offset_device=None, out_row_limit=0, static_weight=False, peer=None,
-         ln_fold=None):
+         ln_fold=None, prefetch=None):
     """a [M,K] (row stride allowed), w [N,K]; returns out [M,N].
 
     `out`, if given, receives the result; with out_rows_per_batch > 0 row m is written at
@@ -32,7 +32,9 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
     static_weight=True promises that `w` is not being written by earlier work still in flight
     on the stream (model weights), which lets the kernel prefetch it early.
     ln_fold=(colsum, bias32, eps), from fold_layernorm(): `a` is the un-normalised input of a
-    LayerNorm and `w` the weight with the LayerNorm scale folded in (M <= 32 only)."""
+    LayerNorm and `w` the weight with the LayerNorm scale folded in (M <= 32 only).
+    prefetch: the weight tensor of the GEMM that will be launched after this one; this launch
+    pulls (the first 64 MB of) it into L2 once its own loads are issued (M <= 128 only)."""
     require_cuda(a, w, bias, residual, out)
     if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1]:
         raise RuntimeError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T do not match")
@@ -52,11 +54,13 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
     if residual is not None and (residual.stride(-1) != 1 or residual.dtype != a.dtype):
         raise RuntimeError("gemm: residual must be row-major and of the operand dtype")
     code = ACT_CODES[act] if not isinstance(act, int) else act
+    if prefetch is not None and M <= 128:
+        lib().eb_gemm_prefetch_hint(ptr(prefetch), min(prefetch.numel() * prefetch.element_size(), PREFETCH_MAX_BYTES))
     nbytes = lib().eb_gemm_workspace_bytes(M, N, K)
     ws = workspace(a.device, nbytes) if nbytes else None
     if ln_fold is not None:
         colsum, bias32, eps = ln_fold
-        if bias is not None or peer is not None and peer.world > 1:
+        if bias is not None or peer is not None:
             raise RuntimeError("gemm: ln_fold carries the bias and does not combine with the peer exchange")
         if colsum.dtype != torch.float32 or bias32.dtype != torch.float32 or colsum.numel() != N or bias32.numel() != N:
             raise RuntimeError("gemm: ln_fold vectors must be fp32 of length N")
@@ -66,7 +70,7 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
                                ptr(out_row_offset_device), int(out_row_limit), 1 if static_weight else 0, ptr(ws),
                                ws.numel() if ws is not None else 0, stream_ptr()), "gemm_ln")
         return out
-    if peer is not None and peer.world > 1:
+    if peer is not None:
         if not peer.fits(M, N):
             raise RuntimeError(f"gemm: {M} x {N} does not fit the peer exchange areas")
         check(lib().eb_gemm_allreduce(ptr(a), a.stride(0), ptr(w), w.stride(0), ptr(out), out_ld, ptr(bias), ptr(residual),
@@ -85,6 +89,7 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
 
 
 LN_FOLD_MAX_ROWS = 32
+PREFETCH_MAX_BYTES = 64 << 20        # about half of L2: what a following launch can expect to still find there
 
 
 def fold_layernorm(weight, bias, gamma, beta):

@@ -53,9 +53,12 @@ class Worker:
             model = model_fn(**model_kwargs)
             self.model = model.cuda() if use_cuda else model
             if use_cuda and tp_world_size > 1:
-                # generation steps exchange their row-parallel partial sums over NVLink peer
-                # memory inside the GEMM kernels; NCCL remains for everything larger
-                ctx.enable_peer_exchange_for(self.model)
+                # the all-reduces of the row-parallel layers run in the library's own kernels over
+                # NVLink peer memory; where the peers' memory cannot be mapped, NCCL carries them
+                try:
+                    ctx.enable_peer_exchange_for(self.model)
+                except RuntimeError:
+                    ctx.peer = None
         except Exception as exc:                       # noqa: BLE001 (sent to the master)
             self.output_pipe.send(RemoteFailure(rank, f"{type(exc).__name__}: {exc}"))
             _stop.wait(10.0)                           # the master tears the RPC layer down

@@ -163,7 +163,7 @@ EB_API int eb_layer_norm_fwd(void *y, float *mean, float *invvar, const void *x,
  * and gather areas of eb_gemm_reduce_scatter / eb_reduce_broadcast, at offsets the caller
  * chooses; eb_comm_local_area returns its local address so that results can be read in place.
  * All ranks must issue the same exchanges in the same order.  A wait on a peer that lasts longer
- * than the budget (1 s unless changed) is abandoned: the kernel records EB_ETIMEDOUT in the
+ * than the budget (5 s unless changed) is abandoned: the kernel records EB_ETIMEDOUT in the
  * context (eb_comm_status) or in the device status word (eb_device_status), its result is then
  * unspecified and the ranks' sequence numbers no longer agree: tear the group down.  One host
  * thread at a time per context; exchanges sharing a context must not overlap on the device. */
@@ -249,6 +249,15 @@ EB_API int eb_gemm(const void *A, long long lda, const void *W, long long ldw, v
             int c_row_offset_limit, int flags, void *workspace, size_t workspace_bytes, void *stream);
 EB_API size_t eb_gemm_workspace_bytes(int M, int N, int K);
 
+/* A hint for the NEXT eb_gemm / eb_gemm_ln / eb_gemm_allreduce launch issued by this host thread:
+ * once that launch has requested all its own tiles, it asks for [next_weights, next_weights +
+ * bytes) to be brought into L2, so that the launch after it (whose weights these are) finds them
+ * there instead of waiting for HBM while its predecessor is still in its epilogue.  Generation
+ * steps are chains of short weight streams with a dependency between each two; this keeps HBM
+ * busy across the gaps.  The hint is consumed by one launch (NULL cancels it); it changes no
+ * result.  No counterpart in the reference (its linear layers call cuBLAS one at a time). */
+EB_API int eb_gemm_prefetch_hint(const void *next_weights, size_t bytes);
+
 /* Row-parallel GEMM with the tensor-parallel all-reduce fused into its epilogue, for the
  * generation orientation (M <= 128).  Replaces "F.linear, then dist.all_reduce, then + bias" of
  * colossalai's Linear1D_Row (the row-parallel layers constructed at
@@ -259,7 +268,8 @@ EB_API size_t eb_gemm_workspace_bytes(int M, int N, int K);
  * rank obtains the bit-identical result; bias, activation and residual are applied after the
  * sum on every rank.  One launch = one exchange of the context (see eb_comm above):
  * eb_comm_exchange_bytes(world, M rounded up to 16 / 32 / 64 / 128, N) must fit half of the
- * receive area, N must be a multiple of 4.  A context of world 1 degenerates to eb_gemm. */
+ * receive area, N must be a multiple of 4.  A context of one rank exchanges with itself (same result
+ * as eb_gemm up to the rounding of the product to the operand type). */
 EB_API int eb_gemm_allreduce(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
                       const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
                       int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,

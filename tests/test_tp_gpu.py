@@ -15,6 +15,30 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def _leave(rank, ret, ok):
+    """Ends a rank.  A rank that failed must not linger in collective teardown while its peer
+    waits for it inside a collective: it reports and exits at once, which lets the spawner end
+    the other rank too."""
+    import sys
+    import traceback
+    import torch.distributed as dist
+    if ok:
+        dist.destroy_process_group()
+        return
+    traceback.print_exc()
+    try:
+        from energonai_b200 import tp
+        from energonai_b200.gemm import device_status
+        peer = tp.get_tp().peer
+        print(f"rank {rank}: device status {device_status(clear=False)}, context status "
+              f"{peer.status(clear=False) if peer is not None else None}", file=sys.stderr, flush=True)
+    except Exception:                                            # noqa: BLE001
+        pass
+    ret[rank] = False
+    sys.stderr.flush()
+    os._exit(1)
+
+
 def _worker(rank, world, port, ret, use_peer=False):
     import torch.distributed as dist
     from oracle import inputs, layers
@@ -69,8 +93,9 @@ def _worker(rank, world, port, ret, use_peer=False):
                 ok = ok and all(torch.equal(gathered[0], t) for t in gathered)
             ok = ok and device_status()[0] == 0
         ret[rank] = ok
-    finally:
-        dist.destroy_process_group()
+    except BaseException:                                        # noqa: BLE001
+        _leave(rank, ret, False)
+    _leave(rank, ret, True)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -125,7 +150,9 @@ def _model_worker(rank, world, port, ret, use_peer=False):
                 both = [torch.empty_like(got_t) for _ in range(world)]
                 dist.all_gather(both, got_t)
                 assert all(torch.equal(both[0], b) for b in both)      # bit-identical on every rank
-            assert ctx.peer.status()[0] == 0
+            bad = torch.tensor([float(ctx.peer.status(clear=False)[0] != 0)], device="cuda")
+            dist.all_reduce(bad)                  # agree on the verdict before anybody may leave
+            assert float(bad) == 0, f"rank {rank}: context status {ctx.peer.status()}"
         model = PipelineModel(vocab_parallel=True, **kw).cuda().eval()
         model.load_state_dict(shard_model_state(full.state_dict(), rank, world, vocab_parallel=True))
         assert model.embed.word_embeddings.weight.shape[0] == 1024 // world
@@ -133,10 +160,19 @@ def _model_worker(rank, world, port, ret, use_peer=False):
         got = model(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1, record=record_tp)
         if use_peer:
             from energonai_b200.gemm import device_status
-            replayed = model(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1)      # captured chain launches
+            replayed = model(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1)      # captured step, fused exchange
+            assert model._decode_state["chain_mode"] is None and model._decode_state["graph"] is not None
+            model.use_decode_chain = True                                                     # the chained form of the step
+            model._decode_state = None
+            chained = model(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1)
             assert model._decode_state["chain_mode"] == "exchange" and model._decode_state["graph"] is not None
+            agree = torch.tensor([float((chained[:, 11:15] == want[:, 11:15]).float().mean())], device="cuda")
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            assert float(agree) >= 0.9
+            bad = torch.tensor([float(device_status(clear=False)[0] != 0)], device="cuda")
+            dist.all_reduce(bad)
+            assert float(bad) == 0, f"rank {rank}: device status {device_status()}"
             assert float((replayed[:, 11:15] == want[:, 11:15]).float().mean()) >= 0.9
-            assert device_status()[0] == 0
             got = replayed
         # prompt-pass logits: the same numbers up to the all-reduce's summation order
         a, b = record_tp["logits"][0].float(), record["logits"][0].float()
@@ -148,8 +184,9 @@ def _model_worker(rank, world, port, ret, use_peer=False):
         dist.all_gather(gathered, got.contiguous())
         ok = ok and all(torch.equal(gathered[0], t) for t in gathered)
         ret[rank] = ok
-    finally:
-        dist.destroy_process_group()
+    except BaseException:                                        # noqa: BLE001
+        _leave(rank, ret, False)
+    _leave(rank, ret, True)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
