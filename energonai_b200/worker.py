@@ -118,6 +118,12 @@ class Worker:
                     out = RemoteFailure(self.global_rank, f"{type(exc).__name__}: {exc}")
                 self.output_pipe.send(TaskEntry(task.uids, out))
         finally:
+            # captured generation steps hold collective kernels: release them before the groups go
+            # (tearing a process group down under a live graph can block)
+            if hasattr(self.model, "_decode_state"):
+                self.model._decode_state = None
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
             trpc.shutdown()
             if dist.is_initialized():
                 dist.destroy_process_group()

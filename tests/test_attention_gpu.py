@@ -33,13 +33,14 @@ def make_mask(B, S, lens, side, dtype):
     return ((1.0 - valid.float()) * -10000.0).to(dtype), valid
 
 
+@pytest.mark.parametrize("impl", ["mma", "tc"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("B,H,S,D,causal,side", [
     (2, 3, 128, 64, True, "left"), (3, 2, 200, 128, True, "left"), (2, 2, 65, 64, True, None),
     (2, 4, 512, 128, True, "left"), (3, 2, 96, 64, False, "right"), (2, 2, 333, 128, False, "right"),
     (1, 1, 1, 64, True, None), (1, 2, 1024, 128, True, None),
 ])
-def test_prefill(B, H, S, D, causal, side, dtype):
+def test_prefill(B, H, S, D, causal, side, dtype, impl):
     from energonai_b200.attention import attention_prefill
     g = torch.Generator(device="cuda").manual_seed(S + D)
     qkv = torch.randn(B, S, 3 * H * D, device="cuda", generator=g).to(dtype)      # fused k|v|q buffer: strided views
@@ -48,13 +49,40 @@ def test_prefill(B, H, S, D, causal, side, dtype):
     if side:
         lens = [S] + [max(1, S // (i + 2)) for i in range(B - 1)]
         mask, valid = make_mask(B, S, lens, side, dtype)
-    out = attention_prefill(q, k, v, D, mask=mask, causal=causal)
+    out = attention_prefill(q, k, v, D, mask=mask, causal=causal, impl=impl)
     ref = reference(q, k, v, D, mask, causal)
     err = (out.float() - ref).abs()
     if side == "left":          # rows of left-padding queries are unspecified (never consumed): compare valid rows
         err = err * valid[:, :, None]
     assert err.max().item() <= TOL[dtype], err.max().item()
     assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,H,Sq,Sk,D,causal", [(2, 3, 100, 356, 128, True), (1, 5, 260, 300, 64, True), (2, 2, 129, 40, 64, False),
+                                                (16, 5, 512, 512, 128, True)])
+def test_prefill_tc_rectangular(B, H, Sq, Sk, D, causal, dtype):
+    """Tensor-core prompt kernel with q_len != kv_len (a prompt continued against cached keys),
+    separate q / k / v / out tensors, a right-side key mask, and the two kernels against each other."""
+    from energonai_b200.attention import attention_prefill
+    from energonai_b200._lib import lib
+    import ctypes
+    g = torch.Generator(device="cuda").manual_seed(Sq * 7 + Sk)
+    q = torch.randn(B, Sq, H * D, device="cuda", generator=g).to(dtype)
+    k = torch.randn(B, Sk, H * D, device="cuda", generator=g).to(dtype)
+    v = torch.randn(B, Sk, H * D, device="cuda", generator=g).to(dtype)
+    lens = [Sk] + [max(Sk - Sq + 1, Sk - 3 * (i + 1)) for i in range(B - 1)]
+    mask, _ = make_mask(B, Sk, lens, "right", dtype)
+    out = attention_prefill(q, k, v, D, mask=mask, causal=causal, impl="tc")
+    ref = reference(q, k, v, D, mask, causal)
+    assert (out.float() - ref).abs().max().item() <= TOL[dtype]
+    other = attention_prefill(q, k, v, D, mask=mask, causal=causal, impl="mma")
+    assert (out.float() - other.float()).abs().max().item() <= 2 * TOL[dtype]
+    again = attention_prefill(q, k, v, D, mask=mask, causal=causal, impl="tc")
+    assert torch.equal(out, again)
+    torch.cuda.synchronize()
+    st = (ctypes.c_int * 4)()
+    assert lib().eb_device_status(st, 0) == 0 and st[0] == 0, list(st)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
@@ -97,4 +125,6 @@ def test_attention_rejects_unsupported():
     from energonai_b200.attention import attention_prefill
     q = torch.randn(1, 8, 96, device="cuda").half()
     with pytest.raises(RuntimeError, match="head_dim"):
-        attention_prefill(q, q, q, 96)
+        attention_prefill(q, q, q, 96, impl="mma")
+    with pytest.raises(RuntimeError, match="head_dim"):
+        attention_prefill(q, q, q, 96, impl="tc")

@@ -15,6 +15,15 @@ def _free_port():
         return s.getsockname()[1]
 
 
+def _mark(rank, what):
+    """Progress line in gpurun_out/ (when that folder exists): shows how far a rank got if a run
+    has to be ended from outside."""
+    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    if os.path.isdir(out):
+        with open(os.path.join(out, f"tp_test_rank{rank}.log"), "a") as f:
+            f.write(what + "\n")
+
+
 def _leave(rank, ret, ok):
     """Ends a rank.  A rank that failed must not linger in collective teardown while its peer
     waits for it inside a collective: it reports and exits at once, which lets the spawner end
@@ -22,10 +31,13 @@ def _leave(rank, ret, ok):
     import sys
     import traceback
     import torch.distributed as dist
+    _mark(rank, f"leaving ok={ok}")
     if ok:
         dist.destroy_process_group()
+        _mark(rank, "process group destroyed")
         return
     traceback.print_exc()
+    _mark(rank, traceback.format_exc())
     try:
         from energonai_b200 import tp
         from energonai_b200.gemm import device_status
@@ -137,8 +149,10 @@ def _model_worker(rank, world, port, ret, use_peer=False):
         record = {}
         want = full(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1, record=record)
         ctx = tp.init_tp(world)
+        _mark(rank, f"model test use_peer={use_peer}: reference tokens done")
         if use_peer:
             ctx.enable_peer_exchange(16, 5120, bulk_rows=512)
+            _mark(rank, "exchange enabled")
             # the stand-alone one-shot all-reduce against NCCL, several sizes and dtypes
             for dt, n in ((torch.float16, 4096), (torch.bfloat16, 1024 * 40), (torch.float32, 20)):
                 t = (torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rank)) * 3).to(dt)
@@ -150,6 +164,7 @@ def _model_worker(rank, world, port, ret, use_peer=False):
                 both = [torch.empty_like(got_t) for _ in range(world)]
                 dist.all_gather(both, got_t)
                 assert all(torch.equal(both[0], b) for b in both)      # bit-identical on every rank
+                _mark(rank, f"one-shot all-reduce {dt} x {n} ok")
             bad = torch.tensor([float(ctx.peer.status(clear=False)[0] != 0)], device="cuda")
             dist.all_reduce(bad)                  # agree on the verdict before anybody may leave
             assert float(bad) == 0, f"rank {rank}: context status {ctx.peer.status()}"
@@ -157,14 +172,18 @@ def _model_worker(rank, world, port, ret, use_peer=False):
         model.load_state_dict(shard_model_state(full.state_dict(), rank, world, vocab_parallel=True))
         assert model.embed.word_embeddings.weight.shape[0] == 1024 // world
         record_tp = {}
+        _mark(rank, "sharded model built")
         got = model(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1, record=record_tp)
+        _mark(rank, "eager generation done")
         if use_peer:
             from energonai_b200.gemm import device_status
             replayed = model(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1)      # captured step, fused exchange
+            _mark(rank, "replayed generation done")
             assert model._decode_state["chain_mode"] is None and model._decode_state["graph"] is not None
             model.use_decode_chain = True                                                     # the chained form of the step
             model._decode_state = None
             chained = model(input_ids=ids, attention_mask=mask, max_tokens=24, top_k=1)
+            _mark(rank, "chained generation done")
             assert model._decode_state["chain_mode"] == "exchange" and model._decode_state["graph"] is not None
             agree = torch.tensor([float((chained[:, 11:15] == want[:, 11:15]).float().mean())], device="cuda")
             dist.all_reduce(agree, op=dist.ReduceOp.MIN)
@@ -183,6 +202,8 @@ def _model_worker(rank, world, port, ret, use_peer=False):
         gathered = [torch.empty_like(got) for _ in range(world)]
         dist.all_gather(gathered, got.contiguous())
         ok = ok and all(torch.equal(gathered[0], t) for t in gathered)
+        model._decode_state = None            # captured graphs hold collective kernels: release them before the group goes
+        torch.cuda.synchronize()
         ret[rank] = ok
     except BaseException:                                        # noqa: BLE001
         _leave(rank, ret, False)
