@@ -6,9 +6,7 @@ import torch
 from ._lib import lib, check, dtype_code, ptr, stream_ptr, require_cuda
 
 _scratch = {}
-_vt_scratch = {}         # transposed-V scratch of the tensor-core prompt kernel, per device
-TC_MIN_ROWS = 64         # below this many query rows a 128-row tile is mostly padding
-TC_MIN_KEYS = 2048       # measured crossover of the two prompt kernels (fp16, head_dim 128, causal)
+TC_MIN_ROWS = 128        # below this many query rows the 256-row CTAs of the tensor-core kernel are mostly padding
 
 
 def _get_scratch(device, nbytes):
@@ -27,20 +25,10 @@ def _bsh_strides(t, head_dim):
     return t.stride(0), t.stride(1)
 
 
-def _get_vt_scratch(device, nbytes):
-    key = torch.device(device).index
-    buf = _vt_scratch.get(key)
-    if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        _vt_scratch[key] = buf
-    return buf
-
-
 def attention_prefill(q, k, v, head_dim, mask=None, causal=True, scale=None, out=None, impl=None):
     """q [B,Sq,H*D], k/v [B,Sk,H*D] (strided views allowed), mask [B,Sk] additive or None.
     Returns out [B,Sq,H*D].  impl: "tc" (tcgen05 kernel), "mma" (mma.sync kernel) or None =
-    "tc" for prompts of at least TC_MIN_ROWS rows against at least TC_MIN_KEYS keys (EB_ATTN_TC=0
-    keeps "mma")."""
+    "tc" for prompts of at least TC_MIN_ROWS rows (EB_ATTN_TC=0 keeps "mma")."""
     require_cuda(q, k, v, mask, out)
     B, Sq, HD = q.shape
     Sk = k.shape[1]
@@ -53,14 +41,12 @@ def attention_prefill(q, k, v, head_dim, mask=None, causal=True, scale=None, out
     qs, ks, vs, os_ = (_bsh_strides(t, head_dim) for t in (q, k, v, out))
     scale = head_dim ** -0.5 if scale is None else scale
     if impl is None:
-        impl = "tc" if Sq >= TC_MIN_ROWS and Sk >= TC_MIN_KEYS and os.environ.get("EB_ATTN_TC", "1") != "0" else "mma"
+        impl = "tc" if Sq >= TC_MIN_ROWS and os.environ.get("EB_ATTN_TC", "1") != "0" else "mma"
     if impl == "tc":
-        nbytes = lib().eb_attention_prefill_scratch_bytes(B, H, Sk, head_dim)
-        scratch = _get_vt_scratch(q.device, nbytes)
         check(lib().eb_attention_prefill_tc(ptr(q), ptr(k), ptr(v), ptr(out), ptr(mask), qs[0], qs[1], ks[0], ks[1], vs[0],
                                             vs[1], os_[0], os_[1], mask.stride(0) if mask is not None else 0, B, H, Sq, Sk,
-                                            head_dim, 1 if causal else 0, float(scale), dtype_code(q.dtype), ptr(scratch),
-                                            scratch.numel(), stream_ptr()), "attention_prefill_tc", launches=2)
+                                            head_dim, 1 if causal else 0, float(scale), dtype_code(q.dtype), stream_ptr()),
+              "attention_prefill_tc")
         return out
     check(lib().eb_attention_prefill(ptr(q), ptr(k), ptr(v), ptr(out), ptr(mask), qs[0], qs[1], ks[0], ks[1], vs[0], vs[1],
                                      os_[0], os_[1], mask.stride(0) if mask is not None else 0, B, H, Sq, Sk, head_dim,

@@ -5,19 +5,23 @@
 //
 // One CTA owns 128 query rows of one (sequence, head) and walks the visible keys in tiles of
 // 128.  Both products run on tcgen05.mma with fp32 accumulators in tensor memory:
-//   S  = Q . K_tile^T    (128 x 128, K = head_dim)   TMEM columns [0, 128) and [128, 256), alternating
-//   PV = P . V_tile      (128 x head_dim, K = 128)    TMEM columns [256, 256 + head_dim)
-// Q and the K tiles arrive by TMA (3-D maps over the [batch][row][head*dim] views, 128-byte
-// swizzle, rows beyond the sequence read as zeros).  The second product needs its B operand with
-// the contraction index (keys) contiguous, i.e. V transposed: a small kernel writes
-// vT[b][h][d][key] once per call into caller-provided scratch, and the V tiles are TMA boxes of
-// that.  Warp roles (192 threads): warp 0 issues TMA, warp 1 issues the MMAs, warps 2-5 are
-// the softmax: thread r owns query row r, reads its score row from TMEM (tcgen05.ld), keeps the
-// running maximum / sum (fp32, log2 domain), writes the probabilities as the 16-bit, swizzled A
-// operand of the second product into shared memory, and accumulates the output row in
-// registers (O = O * alpha + PV, PV read back from TMEM), so nothing in TMEM needs rescaling.
-// The score accumulator is double-buffered: S of tile j+1 is computed while the softmax warps
-// still work on tile j, so they never wait for the first product.
+//   S  = Q . K_tile^T    (128 x 128, K = head_dim)   TMEM columns [t*128, +128) for row tile t
+//   O += P . V_tile      (128 x head_dim, K = 128)    TMEM columns [256 + t*128, +head_dim)
+// Q, K and V tiles arrive by TMA (3-D maps over the [batch][row][head*dim] views, 128-byte
+// swizzle, rows beyond the sequence read as zeros).  V is used as it lies in memory: for the
+// second product the contraction index (keys) runs down the rows of the tile, which the shared-
+// memory descriptor expresses as an N-major B operand, so nothing is transposed.
+// A CTA serves two row tiles (256 query rows).  Warp roles (320 threads): warp 0 issues
+// TMA, warp 1 issues the MMAs, warps 2-5 and 6-9 are the softmax of row tile 0 and 1: thread r
+// owns query row r, reads its score row from TMEM (tcgen05.ld), keeps the running maximum / sum
+// (fp32, log2 domain) and writes the probabilities as the 16-bit, swizzled A operand of the second
+// product into shared memory.  The output row accumulates in TMEM across the key tiles (the
+// second product adds to it).  Its scale is the maximum the row had when it was last rescaled:
+// only when a new tile raises the row maximum by more than 2^8 do the softmax warps read the row
+// back, multiply it and store it again (tcgen05.ld / st), so that in the common case they never
+// wait for the second product and the probabilities stay below 2^8 (fine in fp16 and bf16, the
+// sum is fp32).  The two row tiles alternate on the tensor core: while the softmax warps of one
+// work on their scores, it serves the other.
 //
 // Every mbarrier wait is bounded; a wait that runs out is recorded, the CTA's roles leave (each
 // decision made uniform over the warp first), copies in flight are given time to land, TMEM is
@@ -31,10 +35,20 @@
 namespace eb {
 namespace {
 
-constexpr int kRows = 128;                 // query rows per CTA = UMMA M = TMEM lanes
+constexpr int kRows = 128;                 // query rows per row tile = UMMA M = TMEM lanes
+constexpr int kTiles = 2;                  // row tiles per CTA, each with its own four softmax warps
 constexpr int kKeys = 128;                 // keys per tile
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 64 + kTiles * 128;
+
+// Shared-memory plan per head_dim.  With head_dim 128 everything but a second V stage fits.
+template <int D> struct TcSmem {
+  static constexpr uint32_t kQBytes = (D / 64) * kRows * 128, kKBytes = (D / 64) * kKeys * 128, kVBytes = (D / 64) * kKeys * 128,
+                            kPBytes = 2 * kRows * 128;
+  static constexpr int kVStages = D > 64 ? 1 : 2;
+  static constexpr size_t kTotal = 1024 + 1024 + (size_t)kTiles * kQBytes + 2 * kKBytes + (size_t)kVStages * kVBytes + (size_t)kTiles * kPBytes;
+};
 constexpr float kLog2eTc = 1.4426950408889634f;
+constexpr float kRescaleLog2 = 8.f;         // the accumulated row is rescaled when its maximum grows by more than 2^8
 constexpr unsigned long long kTcWaitNs = 1000ull * 1000ull * 1000ull;
 
 __device__ int g_tc_status[4];             // [0] code, [1] where, [2] block, [3] detail
@@ -117,20 +131,50 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float *v) {
-  uint32_t r[16];
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float *v) {
+  uint32_t r[32];
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+      "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const float *v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+      "%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // K-major tile of 128-byte rows with the 128-byte swizzle; 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t tc_desc(uint32_t addr) {
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// N-major B operand (the contraction index runs down the rows of the tile): 64-column atoms of
+// 8 rows x 128 bytes, swizzled; atoms along N lie atom_stride bytes apart (leading offset), 8-row
+// groups along K 1024 bytes apart.
+__device__ __forceinline__ uint64_t tc_desc_nmajor(uint32_t addr, uint32_t atom_stride) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(atom_stride >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
          ((uint64_t)2 << 61);
 }
 // kind::f16, fp32 accumulate, both operands K-major, M = 128.
@@ -138,99 +182,64 @@ __host__ __device__ constexpr uint32_t tc_idesc(int n, int is_bf16) {
   return (1u << 4) | ((uint32_t)is_bf16 << 7) | ((uint32_t)is_bf16 << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
 }
 
-// Scores of 16 consecutive keys -> logits in the log2 domain: scale, additive mask, -inf for
-// keys this row does not see (behind the diagonal or beyond the sequence).
-template <typename T>
-__device__ __forceinline__ void tile_logits(float (&x)[16], const T *mrow, bool vec, int kbase, int Sk, int vis_end, float scale_log2) {
-  float mf[16];
-  if (mrow && vec && kbase + 16 <= Sk) {
-    Vec16<T> m0, m1;
-    m0.load(mrow + kbase);
-    m1.load(mrow + kbase + 8);
-    float t0[8], t1[8];
-    m0.unpack(t0);
-    m1.unpack(t1);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      mf[e] = t0[e];
-      mf[8 + e] = t1[e];
-    }
-  } else {
-#pragma unroll
-    for (int e = 0; e < 16; ++e) mf[e] = (mrow && kbase + e < Sk) ? to_f32<T>(mrow[kbase + e]) : 0.f;
-  }
-#pragma unroll
-  for (int e = 0; e < 16; ++e) x[e] = kbase + e < vis_end ? x[e] * scale_log2 + mf[e] * kLog2eTc : -INFINITY;
-}
-
-// ---- V transposed: vT[b][h][d][key] --------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(256) transpose_v_kernel(const T *__restrict__ v, T *__restrict__ vt, long long v_bs, long long v_rs,
-                                                          int H, int D, int Sk, int Skp) {
-  __shared__ T tile[64][66];
-  griddep_wait();
-  griddep_launch();
-  const int b = blockIdx.z, col0 = blockIdx.y * 64, key0 = blockIdx.x * 64;     // col = h*D + d
-  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
-  for (int r = ty; r < 64; r += 4) {
-    const int key = key0 + r;
-    tile[r][tx] = key < Sk ? v[b * v_bs + (long long)key * v_rs + col0 + tx] : from_f32<T>(0.f);
-  }
-  __syncthreads();
-  for (int r = ty; r < 64; r += 4) {
-    const int col = col0 + r, key = key0 + tx;
-    if (key < Skp) vt[((long long)b * H * D + col) * Skp + key] = tile[tx][r];
-  }
-}
-
 // ---- the attention kernel ----------------------------------------------------------------------
-// Shared memory (1024-aligned): [1 KB barriers, TMEM slot, abort flag][Q: D/64 sub-tiles of
-// 128 rows x 128 B][2 stages x (K: D/64 sub-tiles | VT: 2 sub-tiles of D rows x 128 B)]
-// [P: 2 sub-tiles of 128 rows x 128 B].
+// Shared memory (1024-aligned): [1 KB barriers, TMEM slot, abort flag][Q: 2 row tiles x D/64
+// sub-tiles of 128 rows x 128 B][K ring: 2 x D/64 sub-tiles][V ring: kVStages x D/64 sub-tiles
+// of 128 key rows x 128 B][P: 2 row tiles x 2 sub-tiles of 128 rows x 128 B].
 template <typename T, int D>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                            const __grid_constant__ CUtensorMap tm_vt, const TcParams p) {
+                            const __grid_constant__ CUtensorMap tm_v, const TcParams p) {
   constexpr int kSub = D / 64;                                   // 64-column sub-tiles of Q / K
-  constexpr uint32_t kQBytes = kSub * kRows * 128, kKBytes = kSub * kKeys * 128, kVBytes = 2 * D * 128;
-  constexpr uint32_t kStageBytes = kKBytes + kVBytes;
+  constexpr int kVStages = TcSmem<D>::kVStages;
+  constexpr uint32_t kQBytes = TcSmem<D>::kQBytes, kKBytes = TcSmem<D>::kKBytes, kVBytes = TcSmem<D>::kVBytes,
+                     kPBytes = TcSmem<D>::kPBytes;
   constexpr uint32_t kTmemCols = 512, kPvCol = 2 * kKeys;
   constexpr int kBf16 = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-  constexpr uint32_t kIdescS = tc_idesc(kKeys, kBf16), kIdescPV = tc_idesc(D, kBf16);
+  constexpr uint32_t kIdescS = tc_idesc(kKeys, kBf16), kIdescPV = tc_idesc(D, kBf16) | (1u << 16);   // bit 16: B is N-major
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = s32(smem_raw);
   uint8_t *smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
   const uint32_t bar0 = s32(bars);
-  const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = bar0 + 24, s_full = bar0 + 40, s_free = bar0 + 56,
-                 p_full = bar0 + 72, pv_full = bar0 + 80, pv_free = bar0 + 88;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 128);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 136);
-  const uint32_t q_addr = s32(smem) + 1024, kv_addr = q_addr + kQBytes, p_addr = kv_addr + 2 * kStageBytes;
-  uint8_t *p_ptr = smem + 1024 + kQBytes + 2 * kStageBytes;
+  // per-ring barriers are indexed by stage, per-row-tile barriers by tile (8 bytes apart)
+  const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 24, v_full = bar0 + 40, v_empty = bar0 + 56,
+                 s_full = bar0 + 72, p_full = bar0 + 88, pv_full = bar0 + 104;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 256);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 264);
+  const uint32_t q_addr = s32(smem) + 1024, k_addr = q_addr + kTiles * kQBytes, v_addr = k_addr + 2 * kKBytes,
+                 p_addr = v_addr + kVStages * kVBytes;
+  uint8_t *p_ptr = smem + 1024 + kTiles * kQBytes + 2 * kKBytes + kVStages * kVBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;   // longest (latest, under the causal mask) tiles first
-  const int q0 = qt * kRows, shift = p.Sk - p.Sq;
-  // keys any row of this CTA may see: all of them, or up to the last row's diagonal
-  const int last_key = p.causal ? min(p.Sk - 1, q0 + kRows - 1 + shift) : p.Sk - 1;
-  const int ntiles = last_key >= 0 ? last_key / kKeys + 1 : 0;
+  const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;   // longest (latest, under the causal mask) blocks first
+  const int q0 = qb * (kTiles * kRows), shift = p.Sk - p.Sq;
+  // key tiles each row tile walks: all of them, or up to its last row's diagonal; none for a
+  // row tile that lies wholly behind the end of the sequence
+  int nt[kTiles], nmax = 0;
+#pragma unroll
+  for (int t = 0; t < kTiles; ++t) {
+    const int qt0 = q0 + t * kRows;
+    const int last_key = p.causal ? min(p.Sk - 1, qt0 + kRows - 1 + shift) : p.Sk - 1;
+    nt[t] = (qt0 < p.Sq && last_key >= 0) ? last_key / kKeys + 1 : 0;
+    nmax = max(nmax, nt[t]);
+  }
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_vt) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
     bar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      bar_init(kv_full + 8 * s, 1);
-      bar_init(kv_empty + 8 * s, 1);
+      bar_init(k_full + 8 * s, 1);
+      bar_init(k_empty + 8 * s, 1);
+      bar_init(v_full + 8 * s, 1);
+      bar_init(v_empty + 8 * s, 1);
       bar_init(s_full + 8 * s, 1);
-      bar_init(s_free + 8 * s, 4);
+      bar_init(p_full + 8 * s, 4);
+      bar_init(pv_full + 8 * s, 1);
     }
-    bar_init(p_full, 4);
-    bar_init(pv_full, 1);
-    bar_init(pv_free, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -248,146 +257,233 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    if (lane == 0 && ntiles > 0) {
-      bar_expect_tx(q_full, kQBytes);
+    if (lane == 0 && nmax > 0) {
+      bar_expect_tx(q_full, kTiles * kQBytes);
 #pragma unroll
-      for (int kb = 0; kb < kSub; ++kb) tma_load_3d(q_addr + kb * kRows * 128, &tm_q, q_full, h * D + kb * 64, q0, b);
-      for (int j = 0; j < ntiles; ++j) {
-        const int s = j & 1;
-        if (j >= 2 && !bar_wait(kv_empty + 8 * s, ((j >> 1) - 1) & 1, abort_flag, 1)) break;
-        const uint32_t dst = kv_addr + s * kStageBytes;
-        bar_expect_tx(kv_full + 8 * s, kStageBytes);
+      for (int t = 0; t < kTiles; ++t)
 #pragma unroll
-        for (int kb = 0; kb < kSub; ++kb) tma_load_3d(dst + kb * kKeys * 128, &tm_k, kv_full + 8 * s, h * D + kb * 64, j * kKeys, b);
+        for (int kb = 0; kb < kSub; ++kb)
+          tma_load_3d(q_addr + t * kQBytes + kb * kRows * 128, &tm_q, q_full, h * D + kb * 64, q0 + t * kRows, b);
+      // K runs one tile ahead of V: its stage is released earlier (after the scores, not after
+      // the value product), and the next scores are what the softmax warps wait for
+      auto load_k = [&](int j) -> bool {
+        const int ks = j & 1;
+        if (j >= 2 && !bar_wait(k_empty + 8 * ks, ((j >> 1) - 1) & 1, abort_flag, 1)) return false;
+        bar_expect_tx(k_full + 8 * ks, kKBytes);
 #pragma unroll
-        for (int a = 0; a < 2; ++a) tma_load_3d(dst + kKBytes + a * D * 128, &tm_vt, kv_full + 8 * s, j * kKeys + a * 64, 0, b * p.H + h);
+        for (int kb = 0; kb < kSub; ++kb)
+          tma_load_3d(k_addr + ks * kKBytes + kb * kKeys * 128, &tm_k, k_full + 8 * ks, h * D + kb * 64, j * kKeys, b);
+        return true;
+      };
+      bool ok = load_k(0);
+      for (int j = 0; j < nmax && ok; ++j) {
+        const int vs = j % kVStages, vu = j / kVStages;
+        if (j + 1 < nmax && !load_k(j + 1)) break;
+        if (j >= kVStages && !bar_wait(v_empty + 8 * vs, (vu - 1) & 1, abort_flag, 9)) break;
+        bar_expect_tx(v_full + 8 * vs, kVBytes);
+#pragma unroll
+        for (int kb = 0; kb < kSub; ++kb)
+          tma_load_3d(v_addr + vs * kVBytes + kb * kKeys * 128, &tm_v, v_full + 8 * vs, h * D + kb * 64, j * kKeys, b);
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0 && ntiles > 0) {
-      // scores of tile t into S buffer t & 1 (its previous occupant, tile t - 2, must have been read)
-      auto issue_scores = [&](int t) -> bool {
-        const int s = t & 1;
-        const uint32_t k_tile = kv_addr + s * kStageBytes;
-        if (!bar_wait(kv_full + 8 * s, (t >> 1) & 1, abort_flag, 3)) return false;
-        if (t >= 2 && !bar_wait(s_free + 8 * s, ((t >> 1) - 1) & 1, abort_flag, 4)) return false;
+    // Per row tile the order is S(0), then for every key tile j, as soon as P(j) is written
+    // (which also says that S(j) has been read): S(j+1) first, so the softmax warps get their
+    // next scores as early as possible, then O += P(j) . V(j).
+    if (lane == 0 && nmax > 0) {
+      auto last_reader = [&](int j) { return (kTiles > 1 && j < nt[kTiles - 1]) ? kTiles - 1 : 0; };
+      auto issue_scores = [&](int t, int j) -> bool {
+        const int ks = j & 1;
+        if (!bar_wait(k_full + 8 * ks, (j >> 1) & 1, abort_flag, 3)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kb = 0; kb < kSub; ++kb) {
-          const uint64_t a = tc_desc(q_addr + kb * kRows * 128), bd = tc_desc(k_tile + kb * kKeys * 128);
+          const uint64_t a = tc_desc(q_addr + t * kQBytes + kb * kRows * 128), bd = tc_desc(k_addr + ks * kKBytes + kb * kKeys * 128);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma(tmem + s * kKeys, a + 2 * k, bd + 2 * k, kIdescS, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) tc_mma(tmem + t * kKeys, a + 2 * k, bd + 2 * k, kIdescS, (kb > 0 || k > 0) ? 1u : 0u);
         }
-        tc_commit(s_full + 8 * s);
+        tc_commit(s_full + 8 * t);
+        if (t == last_reader(j)) tc_commit(k_empty + 8 * ks);
         return true;
       };
-      bool ok = bar_wait(q_full, 0, abort_flag, 2) && issue_scores(0);
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t v_tile = kv_addr + s * kStageBytes + kKBytes;
-        if (j + 1 < ntiles && !issue_scores(j + 1)) break;
-        if (!bar_wait(p_full, j & 1, abort_flag, 5)) break;                      // P of this tile is in shared memory
-        if (j > 0 && !bar_wait(pv_free, (j - 1) & 1, abort_flag, 6)) break;      // PV of the previous tile has been read
-        tc_fence_after();
+      bool ok = bar_wait(q_full, 0, abort_flag, 2);
+      for (int t = 0; t < kTiles && ok; ++t)
+        if (nt[t] > 0) ok = issue_scores(t, 0);
+      for (int j = 0; j < nmax && ok; ++j) {
+        const int vs = j % kVStages, vu = j / kVStages;
+        for (int t = 0; t < kTiles && ok; ++t) {
+          if (j >= nt[t]) continue;
+          ok = bar_wait(p_full + 8 * t, j & 1, abort_flag, 5);
+          if (ok && j + 1 < nt[t]) ok = issue_scores(t, j + 1);
+          ok = ok && bar_wait(v_full + 8 * vs, vu & 1, abort_flag, 10);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-        for (int a2 = 0; a2 < 2; ++a2) {
-          const uint64_t a = tc_desc(p_addr + a2 * kRows * 128), bd = tc_desc(v_tile + a2 * D * 128);
+          for (int a2 = 0; a2 < 2; ++a2) {
+            const uint64_t a = tc_desc(p_addr + t * kPBytes + a2 * kRows * 128);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma(tmem + kPvCol, a + 2 * k, bd + 2 * k, kIdescPV, (a2 > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k) {
+              // 16 keys per instruction: two 8-row groups (2048 bytes) down the V tile
+              const uint64_t bd = tc_desc_nmajor(v_addr + vs * kVBytes + (a2 * 4 + k) * 2048, kKeys * 128);
+              tc_mma(tmem + kPvCol + t * kKeys, a + 2 * k, bd, kIdescPV, (j > 0 || a2 > 0 || k > 0) ? 1u : 0u);
+            }
+          }
+          tc_commit(pv_full + 8 * t);
+          if (t == last_reader(j)) tc_commit(v_empty + 8 * vs);
         }
-        tc_commit(pv_full);
-        tc_commit(kv_empty + 8 * s);
       }
     }
   } else {
-    // ---------------- softmax warps (2..5): thread = query row ----------------
-    const int quarter = warp & 3, row = quarter * 32 + lane, qi = q0 + row;
-    const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16), t_pv = t_lane + kPvCol;
+    // ---------------- softmax warps: 4 per row tile, thread = query row ----------------
+    const int t = (warp - 2) >> 2, quarter = warp & 3, row = quarter * 32 + lane, qi = q0 + t * kRows + row;
+    const int ntiles = nt[t];
+    const uint32_t t_s = tmem + ((uint32_t)(quarter * 32) << 16) + t * kKeys, t_pv = t_s + kPvCol;
+    const uint32_t my_s_full = s_full + 8 * t, my_p_full = p_full + 8 * t, my_pv_full = pv_full + 8 * t;
+    uint8_t *p_row = p_ptr + t * kPBytes + row * 128;
     const T *mrow = p.mask ? reinterpret_cast<const T *>(p.mask) + (long long)b * p.mask_bs : nullptr;
     const int vis_end = p.causal ? min(p.Sk, qi + shift + 1) : p.Sk;               // keys [0, vis_end) are visible to this row
-    float o[D];
-#pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.f;
-    float m_run = -1e30f, l_run = 0.f;
+    float m_ref = -1e30f, l_run = 0.f;      // m_ref: the maximum the accumulated row and l_run are scaled by
     bool alive = ntiles > 0;
     for (int j = 0; j < ntiles && alive; ++j) {
       const int key0 = j * kKeys;
-      const uint32_t t_s = t_lane + (j & 1) * kKeys;
-      if (!__all_sync(0xffffffffu, bar_wait(s_full + 8 * (j & 1), (j >> 1) & 1, abort_flag, 7))) { alive = false; break; }
+      // Work per chunk of 32 keys, decided for the warp as a whole (tensor-memory loads are
+      // warp-wide): 0 = hidden from every row of the warp (behind the diagonal or the end of the
+      // sequence): nothing to read, P = 0; 1 = visible to every row and no mask value set: one
+      // multiply-add and one exponential per key, most chunks of a long prompt; 2 = per-key
+      // work (the chunk the diagonal crosses, chunks with mask values).  Lane l keeps the mask
+      // value of key l of each chunk, in the log2 domain.
+      int cls[kKeys / 32];
+      float mval[kKeys / 32];
+#pragma unroll
+      for (int c = 0; c < kKeys / 32; ++c) {
+        const int kb = key0 + c * 32;
+        float mv = 0.f;
+        if (mrow && kb + lane < p.Sk) mv = to_f32<T>(mrow[kb + lane]) * kLog2eTc;
+        mval[c] = mv;
+        const bool hidden = __all_sync(0xffffffffu, kb >= vis_end);
+        const bool simple = __all_sync(0xffffffffu, kb + 32 <= vis_end && mv == 0.f);
+        cls[c] = hidden ? 0 : (simple ? 1 : 2);
+      }
+      if (!__all_sync(0xffffffffu, bar_wait(my_s_full, j & 1, abort_flag, 7))) { alive = false; break; }
       tc_fence_after();
       // pass 1: the row maximum of this tile (log2 domain, masks applied)
-      float m_tile = -1e30f;
-#pragma unroll 1
-      for (int c = 0; c < kKeys / 16; ++c) {
-        float x[16];
-        tc_ld16(t_s + c * 16, x);
-        tile_logits<T>(x, mrow, p.mask_vec != 0, key0 + c * 16, p.Sk, vis_end, p.scale_log2);
+      float r0 = -INFINITY, r1 = -INFINITY, r2 = -INFINITY, r3 = -INFINITY, m_tile = -1e30f;
 #pragma unroll
-        for (int e = 0; e < 16; ++e) m_tile = fmaxf(m_tile, x[e]);
-      }
-      const float m_new = fmaxf(m_run, m_tile);
-      const float alpha = exp2f(m_run - m_new);
-      // pass 2: probabilities -> the 16-bit A operand of the second product (swizzled rows of 128 bytes)
-      float l_tile = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kKeys / 16; ++c) {
-        float x[16];
-        tc_ld16(t_s + c * 16, x);
-        tile_logits<T>(x, mrow, p.mask_vec != 0, key0 + c * 16, p.Sk, vis_end, p.scale_log2);
-        Vec16<T> lo, hi;
-        float a8[8], b8[8];
+      for (int c = 0; c < kKeys / 32; ++c) {
+        if (cls[c] == 0) continue;
+        float x[32];
+        tc_ld32(t_s + c * 32, x);
+        if (cls[c] == 1) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          a8[e] = exp2f(x[e] - m_new);
-          b8[e] = exp2f(x[8 + e] - m_new);
+          for (int e = 0; e < 32; e += 4) {
+            r0 = fmaxf(r0, x[e]);
+            r1 = fmaxf(r1, x[e + 1]);
+            r2 = fmaxf(r2, x[e + 2]);
+            r3 = fmaxf(r3, x[e + 3]);
+          }
+        } else {
+          const int nvis = vis_end - (key0 + c * 32);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float v = fmaf(x[e], p.scale_log2, __shfl_sync(0xffffffffu, mval[c], e));
+            m_tile = fmaxf(m_tile, e < nvis ? v : -INFINITY);
+          }
         }
-        lo.pack(a8);
-        hi.pack(b8);
-        // the sum runs over the ROUNDED probabilities, the values the second product multiplies
-        lo.unpack(a8);
-        hi.unpack(b8);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) l_tile += a8[e] + b8[e];
-        uint8_t *dst = p_ptr + (c >> 2) * (kRows * 128) + row * 128;
-        const int u = (c & 3) * 2;
-        *reinterpret_cast<uint4 *>(dst + ((u ^ (row & 7)) << 4)) = lo.raw;
-        *reinterpret_cast<uint4 *>(dst + (((u + 1) ^ (row & 7)) << 4)) = hi.raw;
       }
-      // S has been read (twice): the tensor core may overwrite it with the next tile's scores
+      r0 = fmaxf(fmaxf(r0, r1), fmaxf(r2, r3));
+      if (r0 > -INFINITY) m_tile = fmaxf(m_tile, r0 * p.scale_log2);   // the scale is positive: the maximum commutes with it
+      // The previous tile's value product must be complete before P is overwritten (it reads P)
+      // and before the accumulated row is rescaled; it was issued right behind the scores just
+      // read, so this wait is normally over already.
+      if (j > 0 && !__all_sync(0xffffffffu, bar_wait(my_pv_full, (j - 1) & 1, abort_flag, 8))) { alive = false; break; }
+      // rescale only when some row of the warp gained more than 2^8 (the loads and stores of
+      // tensor memory are warp-wide, so the warp decides together)
+      if (__any_sync(0xffffffffu, m_tile > m_ref + kRescaleLog2)) {
+        const float m_new = fmaxf(m_ref, m_tile);
+        const float alpha = ex2(m_ref - m_new);
+        m_ref = m_new;
+        l_run *= alpha;
+        if (j > 0) {
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            float x[32];
+            tc_ld32(t_pv + c * 32, x);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) x[e] *= alpha;
+            tc_st32(t_pv + c * 32, x);
+          }
+          tc_st_wait();
+        }
+      }
+      // pass 2: probabilities -> the 16-bit A operand of the second product (swizzled rows of 128 bytes)
+      float l0 = 0.f, l1 = 0.f;
+      const float neg_m = -m_ref;
+#pragma unroll
+      for (int c = 0; c < kKeys / 32; ++c) {
+        uint8_t *dst = p_row + (c >> 1) * (kRows * 128);
+        if (cls[c] == 0) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4 *>(dst + ((((c & 1) * 4 + g) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+          continue;
+        }
+        float x[32];
+        tc_ld32(t_s + c * 32, x);
+        if (cls[c] == 1) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) x[e] = ex2(fmaf(x[e], p.scale_log2, neg_m));
+        } else {
+          const int nvis = vis_end - (key0 + c * 32);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float v = fmaf(x[e], p.scale_log2, __shfl_sync(0xffffffffu, mval[c], e));
+            x[e] = e < nvis ? ex2(v + neg_m) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack2<T>(x[g * 8 + 0], x[g * 8 + 1]);
+          w.y = pack2<T>(x[g * 8 + 2], x[g * 8 + 3]);
+          w.z = pack2<T>(x[g * 8 + 4], x[g * 8 + 5]);
+          w.w = pack2<T>(x[g * 8 + 6], x[g * 8 + 7]);
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            l0 += x[g * 8 + e];
+            l1 += x[g * 8 + e + 1];
+          }
+          *reinterpret_cast<uint4 *>(dst + ((((c & 1) * 4 + g) ^ (row & 7)) << 4)) = w;
+        }
+      }
+      l_run += l0 + l1;
+      // P is complete for this warp's 32 rows: make it visible to the tensor core's reads.  The
+      // same arrival tells the issuer that S has been read and that the row has been rescaled.
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) bar_arrive(s_free + 8 * (j & 1));
-      // P is complete for this warp's 32 rows: make it visible to the tensor core's reads
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) bar_arrive(p_full);
-      l_run = l_run * alpha + l_tile;
-      m_run = m_new;
-      if (!__all_sync(0xffffffffu, bar_wait(pv_full, j & 1, abort_flag, 8))) { alive = false; break; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < D / 16; ++c) {
-        float x[16];
-        tc_ld16(t_pv + c * 16, x);
-#pragma unroll
-        for (int e = 0; e < 16; ++e) o[c * 16 + e] = o[c * 16 + e] * alpha + x[e];
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) bar_arrive(pv_free);
+      if (lane == 0) bar_arrive(my_p_full);
     }
-    if (alive && qi < p.Sq) {
+    if (alive && !__all_sync(0xffffffffu, bar_wait(my_pv_full, (ntiles - 1) & 1, abort_flag, 11))) alive = false;
+    if (alive) {
+      tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       T *orow = reinterpret_cast<T *>(p.o) + (long long)b * p.o_bs + (long long)qi * p.o_rs + h * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        float x[32];
+        tc_ld32(t_pv + c * 32, x);                 // warp-wide: rows behind the end of the sequence read too, and store nothing
+        if (qi < p.Sq) {
 #pragma unroll
-      for (int c = 0; c < D / 8; ++c) {
-        Vec16<T> pk;
-        float t8[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) t8[e] = o[c * 8 + e] * inv;
-        pk.pack(t8);
-        pk.store(orow + c * 8);
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack2<T>(x[g * 8 + 0] * inv, x[g * 8 + 1] * inv);
+            w.y = pack2<T>(x[g * 8 + 2] * inv, x[g * 8 + 3] * inv);
+            w.z = pack2<T>(x[g * 8 + 4] * inv, x[g * 8 + 5] * inv);
+            w.w = pack2<T>(x[g * 8 + 6] * inv, x[g * 8 + 7] * inv);
+            *reinterpret_cast<uint4 *>(orow + c * 32 + g * 8) = w;
+          }
+        }
       }
     }
   }
@@ -442,7 +538,7 @@ int tc_map3(CUtensorMap *map, const void *base, int dtype, long long cols, long 
 
 template <typename T, int D>
 int launch_tc(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const TcParams &p, cudaStream_t st) {
-  constexpr size_t smem = 1024 + 1024 + (size_t)(D / 64) * kRows * 128 + 2 * ((size_t)(D / 64) * kKeys * 128 + 2 * D * 128) + 2 * kRows * 128;
+  constexpr size_t smem = TcSmem<D>::kTotal;
   auto kern = attention_prefill_tc_kernel<T, D>;
   static bool configured[64] = {};
   int dev = 0;
@@ -454,7 +550,7 @@ int launch_tc(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &m
     }
     configured[dev] = true;
   }
-  dim3 grid((p.Sq + kRows - 1) / kRows, p.H, p.B);
+  dim3 grid((p.Sq + kTiles * kRows - 1) / (kTiles * kRows), p.H, p.B);
   launch_pdl(kern, grid, dim3(kTcThreads), smem, st, mq, mk, mv, p);
   return check_launch("attention_prefill");
 }
@@ -480,18 +576,12 @@ int attention_tc_status(int *out4, bool clear) {
 
 using namespace eb;
 
-extern "C" size_t eb_attention_prefill_scratch_bytes(int batch, int heads, int kv_len, int head_dim) {
-  if (batch <= 0 || heads <= 0 || kv_len <= 0 || head_dim <= 0) return 0;
-  const size_t skp = ((size_t)kv_len + 63) / 64 * 64;
-  return (size_t)batch * heads * head_dim * skp * 2;
-}
-
 extern "C" int eb_attention_prefill_tc(const void *q, const void *k, const void *v, void *out, const void *mask,
                                        long long q_batch_stride, long long q_row_stride, long long k_batch_stride,
                                        long long k_row_stride, long long v_batch_stride, long long v_row_stride,
                                        long long o_batch_stride, long long o_row_stride, long long mask_batch_stride, int batch,
                                        int heads, int q_len, int kv_len, int head_dim, int causal, float scale, int dtype,
-                                       void *scratch, size_t scratch_bytes, void *stream) {
+                                       void *stream) {
   if (batch == 0 || heads == 0 || q_len == 0) return EB_OK;
   EB_REQUIRE(dtype == EB_F16 || dtype == EB_BF16, "attention_prefill: fp16 or bf16 only (dtype %d)", dtype);
   EB_REQUIRE(head_dim == 64 || head_dim == 128, "attention_prefill: head_dim %d not supported (64 or 128)", head_dim);
@@ -503,27 +593,14 @@ extern "C" int eb_attention_prefill_tc(const void *q, const void *k, const void 
                                o_batch_stride, o_row_stride};
   for (long long s : strides) EB_REQUIRE(s % 8 == 0, "attention_prefill: strides must be multiples of 8 elements");
   EB_REQUIRE(kv_len >= q_len || !causal, "attention_prefill: causal attention needs kv_len >= q_len");
-  const size_t need = eb_attention_prefill_scratch_bytes(batch, heads, kv_len, head_dim);
-  EB_REQUIRE(scratch && aligned16(scratch) && scratch_bytes >= need, "attention_prefill: needs a scratch of %zu bytes (eb_attention_prefill_scratch_bytes)", need);
-  const int skp = (kv_len + 63) / 64 * 64;
+  EB_REQUIRE(scale > 0.f, "attention_prefill: the scale must be positive");
   cudaStream_t st = as_stream(stream);
   const long long hd = (long long)heads * head_dim;
-  {
-    dim3 grid(skp / 64, (unsigned)(hd / 64), batch);
-    if (dtype == EB_F16)
-      launch_pdl(transpose_v_kernel<__half>, grid, dim3(256), 0, st, reinterpret_cast<const __half *>(v), reinterpret_cast<__half *>(scratch),
-                 v_batch_stride, v_row_stride, heads, head_dim, kv_len, skp);
-    else
-      launch_pdl(transpose_v_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, reinterpret_cast<const __nv_bfloat16 *>(v),
-                 reinterpret_cast<__nv_bfloat16 *>(scratch), v_batch_stride, v_row_stride, heads, head_dim, kv_len, skp);
-    int rc = check_launch("attention_prefill (transpose)");
-    if (rc) return rc;
-  }
   CUtensorMap mq, mk, mv;
   int rc;
+  if ((rc = tc_map3(&mv, v, dtype, hd, kv_len, batch, v_row_stride, v_batch_stride, kKeys))) return rc;
   if ((rc = tc_map3(&mq, q, dtype, hd, q_len, batch, q_row_stride, q_batch_stride, kRows))) return rc;
   if ((rc = tc_map3(&mk, k, dtype, hd, kv_len, batch, k_row_stride, k_batch_stride, kKeys))) return rc;
-  if ((rc = tc_map3(&mv, scratch, dtype, kv_len, head_dim, (long long)batch * heads, skp, (long long)head_dim * skp, head_dim))) return rc;
   TcParams p{};
   p.B = batch; p.H = heads; p.Sq = q_len; p.Sk = kv_len; p.causal = causal;
   p.scale_log2 = scale * kLog2eTc;

@@ -317,13 +317,11 @@ __device__ __forceinline__ long long c_row_offset(const GemmParams &p, int m) {
 
 // ---- the kernel ---------------------------------------------------------------------------------
 // Shared memory: [1 KB: mbarriers, TMEM slot, flags][stages x kpb x (lane tile | column tile)].
-// MINB = CTAs meant to share an SM.  2 is for generation-step launches whose per-CTA share of the
-// weights is small (a wide tensor-parallel group): with half the shared memory and a register
-// budget that lets two CTAs be resident, the CTAs of the NEXT launch of the stream start while
-// this one is still running (programmatic dependent launch), request their first weight stages
-// and wait; when this launch ends, the next one finds most of its weights already on the SM.
-template <typename T, int BN, bool SWAP, int MINB = 1>
-__global__ void __launch_bounds__(kThreads, MINB)
+// (A form with two CTAs per SM, half the stages each, so that the next launch's CTAs could start
+// their weight stream beside a running launch, was measured on the shard shapes of an 8-way
+// group: 51 us per layer against 36 us.  One CTA per SM it is.)
+template <typename T, int BN, bool SWAP>
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__ CUtensorMap tm_col, const GemmParams p) {
   constexpr uint32_t kColBytes = BN * 128;
   constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
@@ -833,7 +831,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           for (int m = 0; m < BN; ++m) v[m] = 0.f;
           // Collect: the lines of kSrc sources at a time are requested together and their
           // sequence numbers looked at afterwards (a test between two loads would serialise them).
-          constexpr int kSrc = MINB > 1 ? (kLines <= 4 ? 2 : 1) : (kLines <= 4 ? 4 : (kLines <= 8 ? 2 : 1));   // (register budget)
+          constexpr int kSrc = kLines <= 4 ? 4 : (kLines <= 8 ? 2 : 1);   // (register budget)
           for (int r0 = 0; r0 < cm.world && !lost; r0 += kSrc) {
             LlLine got[kSrc][kLines];
             const unsigned char *src = cm.recv[cm.rank] + half + ((unsigned long long)r0 * per_src + (unsigned long long)n * kLines) * 16ull;
@@ -1014,9 +1012,9 @@ int make_map(CUtensorMap *map, const void *base, int dtype, long long rows, long
   return EB_OK;
 }
 
-template <typename T, int BN, bool SWAP, int MINB = 1>
+template <typename T, int BN, bool SWAP>
 int launch(const CUtensorMap &tl, const CUtensorMap &tc, const GemmParams &p, int grid, size_t smem, cudaStream_t st) {
-  auto kern = gemm_kernel<T, BN, SWAP, MINB>;
+  auto kern = gemm_kernel<T, BN, SWAP>;
   static size_t configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1352,10 +1350,7 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
     const size_t stage_bytes = sub_bytes * p.kpb;
     EB_REQUIRE((long long)((N + kLanes - 1) / kLanes) * ((K + kBlockK - 1) / kBlockK) < (1ll << 30), "gemm: N*K too large");
     swap_split(N, K, p.kpb, &grid, &p.units_per_cta);
-    // A CTA whose whole share is a handful of stages (the shards of a wide tensor-parallel group)
-    // runs in the two-per-SM form: 3 stages (108 KB), so that the next launch's CTAs fit beside it.
-    const bool two_per_sm = bn <= 32 && p.units_per_cta <= 8;
-    const size_t budget = (size_t)(two_per_sm ? 112 : 200) * 1024;
+    const size_t budget = (size_t)200 * 1024;
     const size_t fixed = kBarrierBytes + 1024;                      // barriers, alignment
     int stages = (int)((budget - fixed) / stage_bytes);
     stages = stages > kMaxStages ? kMaxStages : (stages < 2 ? 2 : stages);
@@ -1376,16 +1371,11 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
 #define EB_SWAP(BN)                                                                             \
   (dtype == EB_F16 ? launch<__half, BN, true>(tl, tc, p, grid, smem, st)                        \
                    : launch<__nv_bfloat16, BN, true>(tl, tc, p, grid, smem, st))
-#define EB_SWAP2(BN)                                                                            \
-  (dtype == EB_F16 ? launch<__half, BN, true, 2>(tl, tc, p, grid, smem, st)                     \
-                   : launch<__nv_bfloat16, BN, true, 2>(tl, tc, p, grid, smem, st))
-    if (two_per_sm) return bn == 16 ? EB_SWAP2(16) : EB_SWAP2(32);
     if (bn == 16) return EB_SWAP(16);
     if (bn == 32) return EB_SWAP(32);
     if (bn == 64) return EB_SWAP(64);
     return EB_SWAP(128);
 #undef EB_SWAP
-#undef EB_SWAP2
   }
   p.lane_rows = M; p.col_rows = N;
   const long long lane_tiles = (M + kLanes - 1) / kLanes;

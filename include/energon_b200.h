@@ -362,21 +362,18 @@ EB_API int eb_attention_prefill(const void *q, const void *k, const void *v, voi
                          int heads, int q_len, int kv_len, int head_dim, int causal, float scale, int dtype,
                          void *stream);
 
-/* The same product on the tensor cores (tcgen05.mma, accumulators in tensor memory, operands by
- * TMA): the kernel for prompts.  Same arguments and result as eb_attention_prefill (the
- * probabilities are rounded to the tensor dtype before the value product, as the reference's
- * softmax output is), plus a scratch of eb_attention_prefill_scratch_bytes(batch, heads, kv_len,
- * head_dim) bytes (16-byte aligned device memory, contents irrelevant), into which V is
- * transposed once per call so that both products read their operands contraction-major.  One
- * CTA per 128 query rows of a (sequence, head): for q_len well under 128 prefer
- * eb_attention_prefill.  Two launches (transpose + attention). */
-EB_API size_t eb_attention_prefill_scratch_bytes(int batch, int heads, int kv_len, int head_dim);
+/* The same product on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor
+ * memory, Q / K / V tiles by TMA): the kernel for prompts.  Same arguments and result as
+ * eb_attention_prefill (the probabilities are rounded to the tensor dtype before the value
+ * product, as the reference's softmax output is); scale must be positive.  One CTA per 256
+ * query rows of a (sequence, head): for q_len well under 128 prefer eb_attention_prefill.  A
+ * wait that runs out is reported by eb_device_status ("where" codes 100 and up). */
 EB_API int eb_attention_prefill_tc(const void *q, const void *k, const void *v, void *out, const void *mask,
                             long long q_batch_stride, long long q_row_stride, long long k_batch_stride,
                             long long k_row_stride, long long v_batch_stride, long long v_row_stride,
                             long long o_batch_stride, long long o_row_stride, long long mask_batch_stride, int batch,
                             int heads, int q_len, int kv_len, int head_dim, int causal, float scale, int dtype,
-                            void *scratch, size_t scratch_bytes, void *stream);
+                            void *stream);
 
 /* The same product for one new query row per sequence against the cached keys/values (the
  * generation step; replaces the torch.cat past_cache reads of attention.py:86-98 followed by
