@@ -278,7 +278,9 @@ def probe_decode_kernels(model, cfg, st, world, batch):
                 ch.run()
         n_launch = len(chains)
         nbytes = cfg["depth"] * (4 * h * h + 2 * h * cfg["ffn"]) * e / world + cfg["vocab"] * h * e / world
-        name = f"chain_kernel<{tname}, {bn}> (one launch per layer: out-proj, exchange + LayerNorm, FC1, FC2, exchange + LayerNorm, QKV)"
+        steps = ("out-proj, exchange + LayerNorm, FC1, FC2, exchange + LayerNorm, QKV" if world > 1 else
+                 "out-proj, LayerNorm, FC1, FC2, LayerNorm, QKV")
+        name = f"chain_kernel<{tname}, {bn}> (one launch per layer: {steps})"
     else:
         from energonai_b200.gemm import gemm
         from energonai_b200.nn import can_fold

@@ -81,11 +81,6 @@ struct GemmParams {
   int rs;
   long long rs_rpr;
   unsigned long long rs_stage_off;
-  // Optional: once this launch has requested all its own tiles, its producer warps ask for
-  // [pf_ptr, pf_ptr + pf_bytes) to be brought into L2: the weights of the launch that follows,
-  // which then streams them from L2 while this launch is still in its epilogue.
-  const unsigned char *pf_ptr;
-  unsigned long long pf_bytes;
   // swap mode, optional: the A operand is the un-normalised input of a LayerNorm whose scale
   // was multiplied into W beforehand.  The kernel computes each row's mean / inverse std over
   // K itself and the last epilogue of a tile evaluates
@@ -168,10 +163,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
 // Asks for a weight tile to be brought into L2 (no shared-memory destination, no completion).
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
-}
-// Asks for `bytes` (a multiple of 16) at a 16-byte aligned address to be brought into L2.
-__device__ __forceinline__ void prefetch_l2_bulk(const void *ptr, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -442,16 +433,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
       }
     }
     }   // mover lanes
-    // The following launch's weights: 8 KB pieces dealt round-robin over the CTAs and the lanes.
-    if (p.pf_bytes) {
-      constexpr unsigned long long kPiece = 8192;
-      const unsigned long long pieces = (p.pf_bytes + kPiece - 1) / kPiece;
-      for (unsigned long long i = (unsigned long long)blockIdx.x * 32 + lane; i < pieces; i += (unsigned long long)gridDim.x * 32) {
-        const unsigned long long off = i * kPiece;
-        const unsigned long long left = p.pf_bytes - off;
-        prefetch_l2_bulk(p.pf_ptr + off, (uint32_t)(left < kPiece ? left & ~15ull : kPiece));
-      }
-    }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     griddep_wait();
@@ -1253,18 +1234,6 @@ extern "C" int eb_device_status(int *out4, int clear) {
   return EB_OK;
 }
 
-namespace {
-thread_local const void *t_prefetch_ptr = nullptr;
-thread_local size_t t_prefetch_bytes = 0;
-}  // namespace
-
-extern "C" int eb_gemm_prefetch_hint(const void *next_weights, size_t bytes) {
-  EB_REQUIRE(!next_weights || aligned16(next_weights), "gemm_prefetch_hint: the address must be 16-byte aligned");
-  t_prefetch_ptr = next_weights;
-  t_prefetch_bytes = next_weights ? bytes : 0;
-  return EB_OK;
-}
-
 static int gemm_impl(const void *A, long long lda, const void *W, long long ldw, void *C, long long ldc,
                      const void *bias, const void *residual, long long ldr, int M, int N, int K, int dtype,
                      int out_dtype, int act, int c_rows_per_batch, long long c_batch_stride,
@@ -1332,11 +1301,6 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
     p.comm = comm_dev(comm);
   }
   p.bias = bias; p.residual = residual; p.ldr = ldr; p.act = act; p.out_f32 = out_dtype == EB_F32 && dtype != EB_F32;
-  // a hint is consumed by the first launch after it, whatever that launch is
-  p.pf_ptr = reinterpret_cast<const unsigned char *>(t_prefetch_ptr);
-  p.pf_bytes = t_prefetch_bytes & ~(size_t)15;
-  t_prefetch_ptr = nullptr;
-  t_prefetch_bytes = 0;
 
   CUtensorMap tl, tc;
   int rc;

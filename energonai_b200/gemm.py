@@ -21,7 +21,7 @@ def workspace(device, nbytes):
 
 def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out_rows_per_batch=0,
          out_batch_stride=0, out_ld=None, out_row_offset_device=None, out_row_limit=0, static_weight=False, peer=None,
-         ln_fold=None, prefetch=None):
+         ln_fold=None):
     """a [M,K] (row stride allowed), w [N,K]; returns out [M,N].
 
     `out`, if given, receives the result; with out_rows_per_batch > 0 row m is written at
@@ -33,8 +33,9 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
     on the stream (model weights), which lets the kernel prefetch it early.
     ln_fold=(colsum, bias32, eps), from fold_layernorm(): `a` is the un-normalised input of a
     LayerNorm and `w` the weight with the LayerNorm scale folded in (M <= 32 only).
-    prefetch: the weight tensor of the GEMM that will be launched after this one; this launch
-    pulls (the first 64 MB of) it into L2 once its own loads are issued (M <= 128 only)."""
+    (Asking a launch to pull the NEXT launch's weights into L2 was tried and removed: measured on
+    B200 it slowed the generation step at every size, 6.50 -> 6.70 / 7.28 ms for 16 / 64 MB on one
+    GPU and 2.50 -> 2.57 / 2.63 ms on an 8-way shard.)"""
     require_cuda(a, w, bias, residual, out)
     if a.dim() != 2 or w.dim() != 2 or a.shape[1] != w.shape[1]:
         raise RuntimeError(f"gemm: shapes {tuple(a.shape)} x {tuple(w.shape)}^T do not match")
@@ -54,8 +55,6 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
     if residual is not None and (residual.stride(-1) != 1 or residual.dtype != a.dtype):
         raise RuntimeError("gemm: residual must be row-major and of the operand dtype")
     code = ACT_CODES[act] if not isinstance(act, int) else act
-    if prefetch is not None and M <= 128:
-        lib().eb_gemm_prefetch_hint(ptr(prefetch), min(prefetch.numel() * prefetch.element_size(), PREFETCH_MAX_BYTES))
     nbytes = lib().eb_gemm_workspace_bytes(M, N, K)
     ws = workspace(a.device, nbytes) if nbytes else None
     if ln_fold is not None:
@@ -89,7 +88,6 @@ def gemm(a, w, bias=None, act=None, residual=None, out=None, out_dtype=None, out
 
 
 LN_FOLD_MAX_ROWS = 32
-PREFETCH_MAX_BYTES = 64 << 20        # about half of L2: what a following launch can expect to still find there
 
 
 def fold_layernorm(weight, bias, gamma, beta):

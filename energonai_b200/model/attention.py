@@ -148,7 +148,7 @@ class MultiHeadAttention1D(nn.Module):
                 cache.ensure(B, pos + 1, 3 * hl, x.dtype, x.device)
                 buf = cache.buf
                 gemm(x, w, bias=b, static_weight=True, out=buf[:, pos:], out_rows_per_batch=1, out_batch_stride=buf.stride(0),
-                     out_ld=buf.stride(1), ln_fold=fold, prefetch=self.dense.weight)
+                     out_ld=buf.stride(1), ln_fold=fold)
                 cache.len = kv_len = pos + 1
                 ctx = attention_decode(buf[:, :, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, kv_len, mask=mask,
                                        scale=self.scaling, q_in_cache=True)
@@ -158,7 +158,7 @@ class MultiHeadAttention1D(nn.Module):
                 if buf.shape[0] != B:
                     raise RuntimeError("attention: the cache was sized for another batch")
                 gemm(x, w, bias=b, static_weight=True, out=buf, out_rows_per_batch=1, out_batch_stride=buf.stride(0), out_ld=buf.stride(1),
-                     out_row_offset_device=kv_state[0:1], out_row_limit=cap, ln_fold=fold, prefetch=self.dense.weight)
+                     out_row_offset_device=kv_state[0:1], out_row_limit=cap, ln_fold=fold)
                 ctx = attention_decode(buf[:, :, 2 * hl:], buf[:, :, :hl], buf[:, :, hl:2 * hl], d, cap, mask=mask,
                                        scale=self.scaling, q_in_cache=True, kv_len_device=kv_state[1:2])
             ctx = ctx.view(B, 1, hl)

@@ -39,26 +39,6 @@ class Block1D(nn.Module):
         self.norm2 = LayerNorm1D(hidden_size, eps=layernorm_epsilon, dtype=dtype)
         self.mlp = MLP1D(hidden_size=hidden_size, mlp_ratio=mlp_ratio, activation=activation, dtype=dtype, bias=bias,
                          disable_past_cache=disable_past_cache)
-        # Generation steps are a chain of short weight streams: every projection tells its launch
-        # which weights come next, so that they are pulled into L2 while it is still finishing
-        # (out-proj -> FC1 -> FC2 -> the next block's QKV, which the model wires up).
-        fc1, fc2 = self.mlp.dense_1, self.mlp.dense_2
-        self.attn.dense.next_weight = lambda: self._streamed(fc1, self.norm2)
-        fc1.next_weight = lambda: fc2.weight
-        fc2.next_weight = None
-
-    def _streamed(self, lin, norm):
-        """The tensor a generation step really streams for `lin`: its LayerNorm-folded copy once
-        that exists, else the parameter."""
-        val = lin._fold.val
-        return val[0] if (val is not None and self.fold_layernorm and not self.apply_post_layernorm) else lin.weight
-
-    def first_streamed_weight(self):
-        """What this block's first generation-step GEMM (the QKV projection) streams."""
-        val = self.attn._fold.val
-        if val is not None and self.fold_layernorm and not self.apply_post_layernorm:
-            return val[0]
-        return self.attn._packed()[0]
 
     def forward(self, hidden_states, attention_mask=None, first_cache=False, seq_lens=None, kv_state=None):
         """Prompt pass (first_cache=True, or no cache): [batch, seq, hidden] -> same shape.

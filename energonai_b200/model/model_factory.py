@@ -71,12 +71,6 @@ class PipelineModel(nn.Module):
             self.norm = LayerNorm1D(normalized_shape=hidden_size, eps=layernorm_epsilon, dtype=dtype)
             self.head = LMHead1D(hidden_size=hidden_size, vocab_size=vocab_size, bias=False, dtype=dtype,
                                  vocab_parallel=vocab_parallel)
-        # every block's last GEMM announces the weights the next launch will stream (see Block1D)
-        for i, blk in enumerate(self.blocks):
-            if i + 1 < depth:
-                blk.mlp.dense_2.next_weight = self.blocks[i + 1].first_streamed_weight
-            elif last:
-                blk.mlp.dense_2.next_weight = lambda: self.head.weight
 
     def reserve_cache(self, new_tokens):
         """Size the key/value caches so `new_tokens` generation steps need no reallocation."""
@@ -91,10 +85,11 @@ class PipelineModel(nn.Module):
         epilogue); "local" = per layer one attention kernel and one chained kernel for the six
         GEMM / LayerNorm operations around it; "exchange" = the same chain on a tensor-parallel
         group, with the two all-reduces of a layer carried inside it.  The chained forms are
-        opt-in (EB_CHAIN=1): measured on B200 an operation inside the chain costs 12 us at
-        OPT-13B's 8-way shard sizes against 9 us for a launch of its own under programmatic
-        dependent launch, because the grid-wide hand-over between operations (arrival counter,
-        polling, proxy fence) is slower than the hardware's own kernel boundary."""
+        opt-in (EB_CHAIN=1 or use_decode_chain): measured on B200 with OPT-13B they lose, 7.8 ms
+        per step against 6.5 ms on one GPU and 2.97 ms against 2.50 ms on the shard of an 8-way
+        group, because the grid-wide hand-over between operations (arrival counter, polling,
+        proxy fence) is slower than the hardware's own kernel boundary under programmatic
+        dependent launch."""
         from ..tp import get_tp
         tp = get_tp()
         blk = self.blocks[0] if len(self.blocks) else None

@@ -62,17 +62,15 @@ class Linear1D_Col(nn.Module):
         self.bias = nn.Parameter(torch.zeros(self.out_per_rank, dtype=dtype, device=device)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
         self._fold = FoldCache()
-        self.next_weight = None      # callable -> the weight the launch after this one will stream (L2 prefetch hint)
 
     def forward(self, x, act=None, fold_norm=None):
         """fold_norm: the LayerNorm1D whose output this projection would consume; x is then that
         LayerNorm's INPUT and the normalisation happens inside the GEMM (generation steps)."""
-        nxt = self.next_weight() if self.next_weight is not None else None
         if fold_norm is not None:
             w_f, colsum, bias32, eps = self._fold.get(self.weight, self.bias, fold_norm)
-            y = gemm(_flat(x), w_f, act=act, static_weight=True, ln_fold=(colsum, bias32, eps), prefetch=nxt)
+            y = gemm(_flat(x), w_f, act=act, static_weight=True, ln_fold=(colsum, bias32, eps))
         else:
-            y = gemm(_flat(x), self.weight, bias=self.bias, act=act, static_weight=True, prefetch=nxt)
+            y = gemm(_flat(x), self.weight, bias=self.bias, act=act, static_weight=True)
         y = y.view(*x.shape[:-1], self.out_per_rank)
         return get_tp().all_gather_last_dim(y) if self.gather_output else y
 
@@ -86,7 +84,6 @@ class Linear1D_Row(nn.Module):
         self.weight = nn.Parameter(torch.empty(out_features, self.in_per_rank, dtype=dtype, device=device))
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
         nn.init.normal_(self.weight, std=0.02)
-        self.next_weight = None      # see Linear1D_Col
 
     def forward(self, x, residual=None, transient_ok=False):
         """x is this rank's slice of the input features.  Bias (and an optional residual) enter
@@ -99,8 +96,7 @@ class Linear1D_Row(nn.Module):
         if tp.peer is not None and tp.peer.fits(x2.shape[0], self.out_features):
             # generation steps: the all-reduce runs inside the GEMM epilogue over NVLink peer stores
             res = _flat(residual) if residual is not None else None
-            nxt = self.next_weight() if self.next_weight is not None else None
-            y = gemm(x2, self.weight, bias=self.bias, residual=res, static_weight=True, peer=tp.peer, prefetch=nxt)
+            y = gemm(x2, self.weight, bias=self.bias, residual=res, static_weight=True, peer=tp.peer)
             return y.view(*x.shape[:-1], self.out_features)
         if (tp.peer is not None and x2.dtype in (torch.float16, torch.bfloat16)
                 and tp.peer.fits_bulk(x2.shape[0], self.out_features)):
@@ -114,8 +110,7 @@ class Linear1D_Row(nn.Module):
             return y.view(*x.shape[:-1], self.out_features)
         lead = tp.rank == 0
         res = _flat(residual) if (residual is not None and lead) else None
-        nxt = self.next_weight() if self.next_weight is not None else None
-        y = gemm(_flat(x), self.weight, bias=self.bias if lead else None, residual=res, static_weight=True, prefetch=nxt)
+        y = gemm(_flat(x), self.weight, bias=self.bias if lead else None, residual=res, static_weight=True)
         tp.all_reduce(y)
         return y.view(*x.shape[:-1], self.out_features)
 

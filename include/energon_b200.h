@@ -249,15 +249,6 @@ EB_API int eb_gemm(const void *A, long long lda, const void *W, long long ldw, v
             int c_row_offset_limit, int flags, void *workspace, size_t workspace_bytes, void *stream);
 EB_API size_t eb_gemm_workspace_bytes(int M, int N, int K);
 
-/* A hint for the NEXT eb_gemm / eb_gemm_ln / eb_gemm_allreduce launch issued by this host thread:
- * once that launch has requested all its own tiles, it asks for [next_weights, next_weights +
- * bytes) to be brought into L2, so that the launch after it (whose weights these are) finds them
- * there instead of waiting for HBM while its predecessor is still in its epilogue.  Generation
- * steps are chains of short weight streams with a dependency between each two; this keeps HBM
- * busy across the gaps.  The hint is consumed by one launch (NULL cancels it); it changes no
- * result.  No counterpart in the reference (its linear layers call cuBLAS one at a time). */
-EB_API int eb_gemm_prefetch_hint(const void *next_weights, size_t bytes);
-
 /* Row-parallel GEMM with the tensor-parallel all-reduce fused into its epilogue, for the
  * generation orientation (M <= 128).  Replaces "F.linear, then dist.all_reduce, then + bias" of
  * colossalai's Linear1D_Row (the row-parallel layers constructed at
