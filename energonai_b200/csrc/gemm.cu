@@ -1016,6 +1016,11 @@ inline int swap_bn(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 
 // A short K (few stages per tile, the row-parallel GEMMs of a wide tensor-parallel group) is not
 // worth cutting: one CTA streams a whole tile in a few microseconds, which is less than the
 // partial-sum hand-over of a shared tile costs.
+// (Dealing the units evenly over all SMs instead, 148 CTAs rather than the 120-134 that equal
+// whole-unit ranges give on the shard shapes of an 8-way group, was measured slower, 2.75 ms per
+// generation step against 2.63: more CTAs share a tile, and the last arriver's sum of their
+// partial products is on the critical path.  So was a deeper pipeline, 225 KB instead of 200 KB
+// of stages: no difference.)
 constexpr long long kNoSplitStages = 10;
 
 inline void swap_split(int N, int K, int kpb, int *grid, int *units) {

@@ -33,7 +33,7 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
   const int packs_row = S / VEC;   // S % VEC == 0 on this path
   int len = real_len[b];
   len = len < 0 ? 0 : (len > S ? S : len);
-  if (VPL > 0) {
+  if constexpr (VPL > 0) {
     // Only rows that are rewritten are walked (query i < real_len unless ALLROWS): live row r of
     // this batch entry is (head r / live_q, query r % live_q).  With one row at a time the
     // load -> max -> exp -> sum -> store chain left each warp with memory traffic in flight only
@@ -128,8 +128,7 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
 #pragma unroll
       for (int t = 0; t < VPL; ++t) raw_cur[t] = raw_nxt[t];
     }
-    return;
-  }
+  } else {
   for (unsigned rb = warp0; rb < rows_b; rb += nwarps) {
     const int i = (int)(rb % (unsigned)S);
     const long long row = (long long)b * rows_b + rb;
@@ -169,6 +168,7 @@ softmax_kernel(T *__restrict__ scores, const int32_t *__restrict__ real_len, int
         rp[v] = out;
       }
     }
+  }
   }
 }
 
