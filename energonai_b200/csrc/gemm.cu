@@ -70,6 +70,7 @@ struct GemmParams {
   int stages;                    // pipeline depth actually used (<= kMaxStages)
   int kpb;                       // k-blocks (64 columns each) per pipeline stage / barrier hand-over
   int static_w;                  // W may be read before the preceding kernel of the stream has finished
+  int x3d;                       // swap mode: tm_col is a 3-D map [k-block][row][64] of the activations: one copy per stage
   // Fused all-reduce of the generation orientation (comm.world >= 1; a single rank exchanges with itself): the CTA that completes a
   // tile sends this rank's partial product to every rank as flagged lines and adds up what the
   // ranks sent it (see comm.cuh).  A thread's BN batch values of output column n are contiguous
@@ -161,6 +162,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       : "memory");
 }
 // Asks for a weight tile to be brought into L2 (no shared-memory destination, no completion).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
@@ -318,8 +325,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
   constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
   constexpr uint32_t kIdesc = make_idesc(BN, std::is_same<T, __nv_bfloat16>::value ? 1 : 0);
   constexpr uint32_t lane_bytes = kLanes * 128u;
-  const uint32_t sub_bytes = lane_bytes + kColBytes;      // one k-block: lane tile | column tile
-  const uint32_t stage_bytes = sub_bytes * (uint32_t)p.kpb;
+  const uint32_t sub_bytes = lane_bytes + kColBytes;      // one k-block: lane tile + column tile
+  const uint32_t stage_bytes = sub_bytes * (uint32_t)p.kpb;   // a stage: [kpb lane tiles][kpb column tiles]
+  const uint32_t col_base = lane_bytes * (uint32_t)p.kpb;    // offset of the column tiles inside a stage
   const int stages = p.stages, kpb = p.kpb;
   const int nsk = (p.kblocks + kpb - 1) / kpb;             // stages' worth of K per output tile
 
@@ -379,13 +387,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
     // waiting for that kernel; activations always follow the wait.
     const CUtensorMap *tm_w = SWAP ? &tm_lane : &tm_col;
     const CUtensorMap *tm_x = SWAP ? &tm_col : &tm_lane;
-    const uint32_t w_off = lane * sub_bytes + (SWAP ? 0u : lane_bytes);
-    const uint32_t x_off = lane * sub_bytes + (SWAP ? lane_bytes : 0u);
+    const uint32_t lane_off = lane * lane_bytes, colt_off = col_base + lane * kColBytes;
+    const uint32_t w_off = SWAP ? lane_off : colt_off;
+    const uint32_t x_off = SWAP ? colt_off : lane_off;
+    // The activation tiles of the swapped orientation are small (batch rows x 128 bytes), and a
+    // TMA copy of such a box costs about 0.3 us whatever its size: with one copy per k-block the
+    // stages of a CTA became ready 0.6 us apart although their weights had long arrived.  With a
+    // 3-D view [k-block][row][64 columns] of the activations one copy brings all kpb tiles of a stage.
+    const bool x3d = SWAP && p.x3d;
     const bool mover = lane < kpb;
     const uint32_t movers_mask = kpb >= 32 ? 0xffffffffu : ((1u << kpb) - 1u);
     if (mover) {
     const int last_valid = p.kblocks - (nsk - 1) * kpb;                   // k-blocks in the last stage of a tile
-    const uint32_t full_tx = stage_bytes, last_tx = (uint32_t)last_valid * sub_bytes;
+    const uint32_t full_tx = stage_bytes;
+    const uint32_t last_tx = x3d ? (uint32_t)last_valid * lane_bytes + (uint32_t)kpb * kColBytes : (uint32_t)last_valid * sub_bytes;
     int pre = 0;
     if (!p.static_w) griddep_wait();
     {
@@ -427,8 +442,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
         const int kb = sk * kpb + lane;
         if (mover && kb < p.kblocks) {
           if (fresh) tma_load_2d(dst + w_off, tm_w, fb, kb * kBlockK, w_row);
-          tma_load_2d(dst + x_off, tm_x, fb, kb * kBlockK, x_row);
+          if (!x3d) tma_load_2d(dst + x_off, tm_x, fb, kb * kBlockK, x_row);
         }
+        if (x3d && lane == 0) tma_load_3d(dst + col_base, tm_x, fb, 0, x_row, sk * kpb);   // k-blocks beyond K read as zeros
         if (++stage == stages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -450,8 +466,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, 3)) { ok = false; break; }
           tcgen05_fence_after();
           for (int j = 0; j < kpb && sk * kpb + j < p.kblocks; ++j) {
-            const uint32_t a_addr = tiles_addr + stage * stage_bytes + j * sub_bytes;
-            const uint64_t a_desc = make_smem_desc(a_addr), b_desc = make_smem_desc(a_addr + lane_bytes);
+            const uint32_t st_addr = tiles_addr + stage * stage_bytes;
+            const uint64_t a_desc = make_smem_desc(st_addr + j * lane_bytes), b_desc = make_smem_desc(st_addr + col_base + j * kColBytes);
 #pragma unroll
             for (int k = 0; k < kBlockK / kUmmaK; ++k) {
               // advancing 16 elements along K inside the swizzle atom = +32 bytes = +2 in the address field
@@ -993,6 +1009,23 @@ int make_map(CUtensorMap *map, const void *base, int dtype, long long rows, long
   return EB_OK;
 }
 
+// 3-D view of a [rows][K] matrix, K a multiple of 64: (column in k-block, row, k-block); one box
+// holds `blocks` consecutive k-blocks of `box_rows` rows, each written as a swizzled tile of
+// 128-byte rows like make_map's, the tiles one after the other.
+int make_map_blocks(CUtensorMap *map, const void *base, int dtype, long long rows, long long K, long long ld, int box_rows, int blocks) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(EB_ECUDA, "gemm: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {(cuuint64_t)kBlockK, (cuuint64_t)rows, (cuuint64_t)(K / kBlockK)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)kBlockK * 2};
+  cuuint32_t box[3] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows, (cuuint32_t)blocks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dtype == EB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(EB_ECUDA, "gemm: cuTensorMapEncodeTiled (3-D) failed with CUresult %d", (int)r);
+  return EB_OK;
+}
+
 template <typename T, int BN, bool SWAP>
 int launch(const CUtensorMap &tl, const CUtensorMap &tc, const GemmParams &p, int grid, size_t smem, cudaStream_t st) {
   auto kern = gemm_kernel<T, BN, SWAP>;
@@ -1336,7 +1369,12 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
     p.partial = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + kCounterBytes);
     p.lane_rows = N; p.col_rows = M;
     if ((rc = make_map(&tl, W, dtype, N, K, ldw, kLanes))) return rc;
-    if ((rc = make_map(&tc, A, dtype, M, K, lda, bn))) return rc;
+    p.x3d = (K % kBlockK == 0 && p.kpb > 1) ? 1 : 0;
+    if (p.x3d) {
+      if ((rc = make_map_blocks(&tc, A, dtype, M, K, lda, bn, p.kpb))) return rc;
+    } else if ((rc = make_map(&tc, A, dtype, M, K, lda, bn))) {
+      return rc;
+    }
 #define EB_SWAP(BN)                                                                             \
   (dtype == EB_F16 ? launch<__half, BN, true>(tl, tc, p, grid, smem, st)                        \
                    : launch<__nv_bfloat16, BN, true>(tl, tc, p, grid, smem, st))
