@@ -481,7 +481,11 @@ def init_group(cfg, bulk_rows):
         if os.environ.get("EB_PEER", "1") != "0":
             # the all-reduces run inside the library's own kernels over NVLink peer memory
             try:
-                bulk = bulk_rows if os.environ.get("EB_PEER_PROMPT", "1") != "0" else 0
+                # prompt-sized all-reduces: the library's reduce-scatter + reduce/broadcast up to 4 ranks
+                # (measured 63 ms against NCCL's 69 ms per prompt pass at N = 4, equal at N = 2); among
+                # 8 ranks it was erratic (50 to 170 ms against NCCL's 58 ms), so NCCL carries them there
+                default = "1" if world <= 4 else "0"
+                bulk = bulk_rows if os.environ.get("EB_PEER_PROMPT", default) != "0" else 0
                 ctx.enable_peer_exchange(128, cfg["hidden"], bulk_rows=bulk)
                 kind = ("prompt pass: " + ("reduce-scatter in the GEMM epilogue + reduce/broadcast kernel, NVLink peer stores"
                                           if bulk else "NCCL all-reduce") +

@@ -45,6 +45,7 @@ constexpr int kThreads = 192;
 constexpr int kGroup = 16;       // raster group height (lane-side tiles) in normal mode
 constexpr unsigned long long kWaitBudgetNs = 1000ull * 1000ull * 1000ull;
 constexpr int kMaxStages = 32;
+constexpr int kXposeMaxLines = 8;            // fused exchange: widest per-thread line count that is sent through shared memory
 constexpr uint32_t kBarrierBytes = 1024;      // head of shared memory: mbarriers, TMEM slot, abort flag
 
 __device__ int g_status[4];      // [0] code (0 = ok), [1] where, [2] block, [3] detail
@@ -341,6 +342,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const uint32_t epi_bar = tempty_bar + 16;
   const uint32_t tiles_addr = smem_u32(smem) + kBarrierBytes;
+  // behind the stages: per epilogue warp, the lines of a fused exchange on their way out (see the epilogue)
+  uint8_t *xpose = smem + kBarrierBytes + (size_t)p.stages * stage_bytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -795,8 +798,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
           }
         }
         bool lost = false;
-        if (do_epilogue && p.comm.world >= 1 && n_ok) {
-          // Fused all-reduce: this thread holds the rank's complete partial products of output
+        if (do_epilogue && p.comm.world >= 1) {        // (warp-uniform: every lane of the warp is here or none)
+          // Fused all-reduce: a thread holds the rank's complete partial products of output
           // column n for every batch row.  They go to every rank (this one included) as flagged
           // lines, rounded to the operand type (what an all-reduce of the product would carry);
           // then the lines of all sources are collected from the local area and added in rank
@@ -818,12 +821,47 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
               packed[q * 4 + 0] = pk.raw.x; packed[q * 4 + 1] = pk.raw.y;
               packed[q * 4 + 2] = pk.raw.z; packed[q * 4 + 3] = pk.raw.w;
             }
-            const unsigned long long mine = half + ((unsigned long long)cm.rank * per_src + (unsigned long long)n * kLines) * 16ull;
-            for (int r = 0; r < cm.world; ++r) {
+            if (kLines <= kXposeMaxLines) {
+              // The lines of a warp's 32 columns are one contiguous piece of every rank's area,
+              // but a thread's own lines lie 16 * kLines bytes from its neighbour's: stored
+              // straight from the registers, every 16-byte line was a transaction of its own on
+              // NVLink (an exchange among 8 ranks took 16 us, several times what its bytes need).
+              // The warp lays its lines out in shared memory and sends them with consecutive
+              // lanes writing consecutive lines: 512 contiguous bytes per store instruction.
+              unsigned long long *stage = reinterpret_cast<unsigned long long *>(xpose) + (size_t)quarter * (32 * kLines * 2);
+              if (n_ok) {
 #pragma unroll
-              for (int q = 0; q < kLines; ++q) ll_store(cm.recv[r] + mine + q * 16, packed[2 * q], packed[2 * q + 1], comm_seq);
+                for (int q = 0; q < kLines; ++q) {
+                  stage[(lane * kLines + q) * 2] = ((unsigned long long)comm_seq << 32) | packed[2 * q];
+                  stage[(lane * kLines + q) * 2 + 1] = ((unsigned long long)comm_seq << 32) | packed[2 * q + 1];
+                }
+              }
+              __syncwarp();
+              const int n0 = s.lane_row0 + quarter * 32;                      // the warp's first column
+              const int warp_lines = (p.N - n0 < 32 ? (p.N - n0 > 0 ? p.N - n0 : 0) : 32) * kLines;
+              const unsigned long long piece = half + ((unsigned long long)cm.rank * per_src + (unsigned long long)n0 * kLines) * 16ull;
+              for (int rr = 0; rr < cm.world; ++rr) {
+                int r = cm.rank + rr;                                          // every rank starts with another peer
+                if (r >= cm.world) r -= cm.world;
+#pragma unroll
+                for (int it = 0; it < kLines; ++it) {
+                  const int c = it * 32 + lane;                                // line c of the warp's piece
+                  if (c < warp_lines)
+                    asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1, %2};" ::"l"(cm.recv[r] + piece + (unsigned long long)c * 16ull),
+                                 "l"(stage[c * 2]), "l"(stage[c * 2 + 1])
+                                 : "memory");
+                }
+              }
+              __syncwarp();
+            } else if (n_ok) {
+              const unsigned long long mine = half + ((unsigned long long)cm.rank * per_src + (unsigned long long)n * kLines) * 16ull;
+              for (int r = 0; r < cm.world; ++r) {
+#pragma unroll
+                for (int q = 0; q < kLines; ++q) ll_store(cm.recv[r] + mine + q * 16, packed[2 * q], packed[2 * q + 1], comm_seq);
+              }
             }
           }
+          if (n_ok) {
 #pragma unroll
           for (int m = 0; m < BN; ++m) v[m] = 0.f;
           // Collect: the lines of kSrc sources at a time are requested together and their
@@ -869,6 +907,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_lane, const __grid_constant__
                   v[4 * q] += lo.x; v[4 * q + 1] += lo.y; v[4 * q + 2] += hi.x; v[4 * q + 3] += hi.y;
                 }
               }
+          }
           }
         }
         // a peer's lines never came: the whole warp leaves together (lanes without a column of
@@ -1353,7 +1392,9 @@ static int gemm_impl(const void *A, long long lda, const void *W, long long ldw,
     EB_REQUIRE((long long)((N + kLanes - 1) / kLanes) * ((K + kBlockK - 1) / kBlockK) < (1ll << 30), "gemm: N*K too large");
     swap_split(N, K, p.kpb, &grid, &p.units_per_cta);
     const size_t budget = (size_t)200 * 1024;
-    const size_t fixed = kBarrierBytes + 1024;                      // barriers, alignment
+    // a fused exchange of up to 32 batch rows stages its outgoing lines per epilogue warp: 4 x 32 x (bn / 4) x 16 bytes
+    const size_t xpose_bytes = (p.comm.world >= 1 && bn / 4 <= kXposeMaxLines) ? (size_t)512 * bn : 0;
+    const size_t fixed = kBarrierBytes + 1024 + xpose_bytes;        // barriers, alignment, exchange staging
     int stages = (int)((budget - fixed) / stage_bytes);
     stages = stages > kMaxStages ? kMaxStages : (stages < 2 ? 2 : stages);
     p.stages = stages;

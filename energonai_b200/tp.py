@@ -34,6 +34,8 @@ class TPContext:
         cols = [m.out_features for m in model.modules() if isinstance(m, Linear1D_Row)]
         if self.world_size <= 1 or not cols:
             return None
+        if self.world_size > 4:
+            bulk_rows = 0      # among 8 ranks the prompt-sized exchange was measured erratic: NCCL carries prompts there
         return self.enable_peer_exchange(max_rows, max(cols), bulk_rows=bulk_rows)
 
     def all_reduce(self, t):
