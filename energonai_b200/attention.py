@@ -56,12 +56,15 @@ def attention_prefill(q, k, v, head_dim, mask=None, causal=True, scale=None, out
 
 
 def pick_nsplit(batch, heads, kv_len, sm_count=148):
-    """The fewest key splits that still give every SM its three resident CTAs (splitting costs a
-    merge and shortens the per-CTA stream: measured 35.5 / 38.6 / 40.7 us for 1 / 2 / 3 splits at
-    batch 16 x 40 heads x 576 keys), never more than one split per 64-key tile."""
+    """Key splits per (sequence, head).  Splitting costs a merge and shortens every CTA's stream,
+    and was measured to lose whenever a CTA would be left with fewer than about a thousand keys:
+    at 576 keys and batch 16, 1 / 2 / 3 / 6 splits take 30.9 / 34.7 / 36.2 / 41.3 us per layer with
+    40 heads and 7.9 / 9.1 / 9.7 / 10.0 us with the 5 heads of an 8-way shard (80 CTAs on 148 SMs:
+    even an underfilled machine prefers whole streams).  So: one split per 1024 keys, never more
+    than gives every SM its three resident CTAs, never more than one per 64-key tile."""
     tiles = max(1, (kv_len + 63) // 64)
     want = -(-3 * sm_count // max(1, batch * heads))
-    return max(1, min(want, tiles, 64))
+    return max(1, min(want, kv_len // 1024, tiles, 64))
 
 
 def attention_decode(q, k, v, head_dim, kv_len, mask=None, scale=None, out=None, nsplit=None, kv_len_device=None,
