@@ -191,11 +191,27 @@ class PipelineModel(nn.Module):
             st["tok"].copy_(tok)
             st["kv_state"].add_(1)
             return
-        pos_long = st["kv_state"][0:1].to(torch.long)
-        hidden = self.embed.word_embeddings(st["tok"].view(-1, 1)) + self.embed.position_embeddings(pos_long).unsqueeze(0)
+        fused = st.get("hidden") is not None
+        if fused:
+            hidden = st["hidden"]               # the new token's embedding, left there by the previous step's tail
+        else:
+            pos_long = st["kv_state"][0:1].to(torch.long)
+            hidden = self.embed.word_embeddings(st["tok"].view(-1, 1)) + self.embed.position_embeddings(pos_long).unsqueeze(0)
         for block in self.blocks:
             hidden = block(hidden_states=hidden, attention_mask=st["mask4"], first_cache=False, kv_state=st["kv_state"])
         logits = self._last_logits(hidden)
+        if fused:
+            # one launch: arg-max, the token into its column, its embedding for the next step, positions advanced
+            from ..step import greedy_step
+            from ..tp import get_tp
+            we = self.embed.word_embeddings
+            split = getattr(we, "vocab_start", None) is not None
+            greedy_step(logits, st["out_ids"], st["tok"], st["kv_state"], st["step_counter"], word_emb=we.weight,
+                        pos_emb=self.embed.position_embeddings.weight, hidden_out=st["hidden"].view(-1, self.hidden_size),
+                        vocab_start=we.vocab_start if split else 0, add_pos=(not split) or get_tp().rank == 0)
+            if split:
+                get_tp().all_reduce(st["hidden"])
+            return
         tok = logits.argmax(-1)
         st["out_ids"].index_copy_(1, st["kv_state"][1:2].to(torch.long), tok.view(-1, 1))   # the new token's index
         st["tok"].copy_(tok)
@@ -221,6 +237,13 @@ class PipelineModel(nn.Module):
                   "tok": torch.empty((batch_size,), dtype=ids_dtype, device=dev),
                   "kv_state": torch.zeros(2, dtype=torch.int32, device=dev),
                   "chain_mode": self._chain_mode(batch_size, model_dtype)}
+            # the step's tail as one launch (eb_greedy_step) needs int64 ids, no token-type table
+            # and logits of the embedding's dtype; otherwise the framework's kernels do it
+            if (st["chain_mode"] is None and ids_dtype == torch.int64 and self.embed.tokentype_embeddings is None
+                    and self.embed.position_embeddings.weight.dtype == model_dtype
+                    and os.environ.get("EB_FUSED_TAIL", "1") != "0"):
+                st["hidden"] = torch.empty((batch_size, 1, self.hidden_size), dtype=model_dtype, device=dev)
+                st["step_counter"] = torch.zeros(1, dtype=torch.int32, device=dev)
             self._decode_state = st
         return st
 
@@ -281,6 +304,8 @@ class PipelineModel(nn.Module):
         out_ids[:, cur_len] = tok
         st["tok"].copy_(tok)
         st["kv_state"].copy_(torch.tensor([cur_len, cur_len + 1], dtype=torch.int32), non_blocking=False)
+        if st.get("hidden") is not None:    # the first generated token's embedding; later ones come from the step's tail
+            st["hidden"].copy_(self.embed(tok.view(-1, 1), past_key_values_length=cur_len))
         use_graph = greedy and self.use_cuda_graph and (record is None or record.get("allow_graph", False))
         produced = cur_len + 1
         checked = cur_len + 1                                  # columns of out_ids already tested for the stop condition

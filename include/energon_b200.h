@@ -335,6 +335,25 @@ EB_API int eb_decode_chain(const eb_chain_op *ops, int n_ops, int M, int dtype, 
                     size_t workspace_bytes, eb_comm *comm, void *stream);
 EB_API size_t eb_decode_chain_workspace_bytes(const eb_chain_op *ops, int n_ops, int M);
 
+/* ---- the tail of a greedy generation step ----------------------------------------------------- */
+
+/* Replaces, per step, the arg-max / concatenate / embed sequence of the reference's generation
+ * loop (energonai/model/model_factory.py:124-131, energonai/model/embedding.py:44-57) by one launch:
+ *   token[b]   = argmax_v logits[b][v]                      (lowest index among equal maxima)
+ *   tok[b]     = token[b]  (if tok != NULL);  out_ids[b][kv_state[1]] = token[b]  (if that column < out_cols)
+ *   hidden_out[b][:] = word_emb[token[b] - vocab_start][:] (zero if the token belongs to another
+ *                      rank's slice of the vocabulary) + pos_emb[kv_state[0] + 1][:] (if add_pos)
+ *   kv_state[0] += 1; kv_state[1] += 1                      (after every sequence has read them)
+ * kv_state = {position of the token the step just processed, column of out_ids for the new token},
+ * device int32[2]; counter: one device int32, zero between launches.  `dtype` is the logits' type,
+ * `emb_dtype` that of the embedding tables and of hidden_out; word_emb == NULL skips the embedding.  With the vocabulary split over a
+ * tensor-parallel group every rank passes its own slice and exactly one rank passes add_pos = 1;
+ * the all-reduce of hidden_out that follows completes the sum. */
+EB_API int eb_greedy_step(const void *logits, long long ld_logits, int batch, int vocab, int dtype, int64_t *out_ids,
+                   long long ld_out, int out_cols, int64_t *tok, int32_t *kv_state, const void *word_emb,
+                   long long vocab_start, int vocab_rows, const void *pos_emb, int pos_rows, int add_pos, int hidden,
+                   int emb_dtype, void *hidden_out, long long ld_hidden, int32_t *counter, void *stream);
+
 /* ---- fused attention ----------------------------------------------------------------------- */
 
 /* Replaces the score / mask / softmax / value products of MultiHeadAttention1D.forward

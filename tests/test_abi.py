@@ -111,3 +111,15 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libenergon_b200.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.lib()
+
+
+def test_generation_attention_split_rule():
+    """Key splits of the generation-step attention: none below a thousand keys per CTA (measured
+    to lose there), never more than one per 64-key tile or than three CTAs per SM need."""
+    from energonai_b200.attention import pick_nsplit
+    assert [pick_nsplit(16, h, 640) for h in (5, 10, 20, 40)] == [1, 1, 1, 1]
+    assert pick_nsplit(1, 40, 8192) == 8
+    assert pick_nsplit(2, 5, 4096) == 4
+    assert pick_nsplit(8, 96, 2048) == 1          # 768 (sequence, head) pairs fill the machine already
+    assert pick_nsplit(1, 1, 100) == 1
+    assert pick_nsplit(1, 1, 1 << 20) == 64

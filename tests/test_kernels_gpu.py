@@ -253,3 +253,54 @@ def test_layer_norm_module_matches_reference_interface():
     assert (y.float() - ref).abs().max() < 4e-3
     with pytest.raises(RuntimeError):
         ln(torch.randn(2, 9, 255, dtype=torch.float16).cuda())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,V,h,split", [(16, 50272, 5120, False), (3, 1001, 96, False), (5, 4096, 256, True), (1, 7, 8, False)])
+def test_greedy_step_tail(B, V, h, split, dtype):
+    """eb_greedy_step against the framework's arg-max / index / embedding sequence
+    (energonai/model/model_factory.py:124-131, embedding.py:44-57): tokens, the written column, the
+    next step's embedding (bit-exact: one rounded sum of the same two table rows) and the advanced
+    position scalars; with the vocabulary split in two, the halves' outputs add up to the whole."""
+    from energonai_b200.step import greedy_step
+    g = torch.Generator(device="cuda").manual_seed(V + h)
+    logits = torch.randn(B, V, device="cuda", generator=g).to(dtype)
+    logits[0, V // 2] = logits[0, V - 1] = 50.0                       # a tie: the lower index wins
+    word = torch.randn(V, h, device="cuda", generator=g).to(dtype)
+    posw = torch.randn(40, h, device="cuda", generator=g).to(dtype)
+    cols, pos = 12, 8
+    out_ids = torch.full((B, cols), -1, dtype=torch.int64, device="cuda")
+    tok = torch.empty(B, dtype=torch.int64, device="cuda")
+    kv = torch.tensor([pos, pos + 1], dtype=torch.int32, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    want_tok = logits.float().argmax(-1)
+    assert want_tok[0].item() == V // 2
+    want_hidden = (word[want_tok].float() + posw[pos + 1].float()).to(dtype)
+    if not split:
+        hidden = torch.empty(B, 1, h, dtype=dtype, device="cuda")
+        greedy_step(logits, out_ids, tok, kv, counter, word_emb=word, pos_emb=posw, hidden_out=hidden.view(B, h))
+        assert torch.equal(hidden.view(B, h), want_hidden)
+    else:
+        half = V // 2
+        parts = []
+        for r in range(2):
+            kv_r = torch.tensor([pos, pos + 1], dtype=torch.int32, device="cuda")
+            hidden = torch.empty(B, h, dtype=dtype, device="cuda")
+            greedy_step(logits, out_ids, tok, kv_r if r else kv, counter, word_emb=word[r * half:(r + 1) * half].contiguous(),
+                        pos_emb=posw, hidden_out=hidden, vocab_start=r * half, add_pos=(r == 0))
+            parts.append(hidden.float())
+        assert torch.equal((parts[0] + parts[1]).to(dtype), want_hidden)
+    assert torch.equal(tok, want_tok)
+    assert torch.equal(out_ids[:, pos + 1], want_tok) and (out_ids[:, :pos + 1] == -1).all() and (out_ids[:, pos + 2:] == -1).all()
+    assert kv.tolist() == [pos + 1, pos + 2] and counter.item() == 0
+    if not split and dtype != torch.float32:
+        # fp32 logits (what the LM head of a generation step produces) beside 16-bit tables
+        hidden2 = torch.empty(B, h, dtype=dtype, device="cuda")
+        kv2 = torch.tensor([pos, pos + 1], dtype=torch.int32, device="cuda")
+        greedy_step(logits.float(), out_ids, tok, kv2, counter, word_emb=word, pos_emb=posw, hidden_out=hidden2)
+        assert torch.equal(tok, want_tok) and torch.equal(hidden2, want_hidden)
+    # a column outside the output is not written, and nothing else breaks
+    kv.copy_(torch.tensor([pos, cols], dtype=torch.int32))
+    before = out_ids.clone()
+    greedy_step(logits, out_ids, tok, kv, counter)
+    assert torch.equal(out_ids, before) and kv.tolist() == [pos + 1, cols + 1]
