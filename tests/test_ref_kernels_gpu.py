@@ -148,7 +148,7 @@ def test_padding_kernels_against_the_reference_kernels(ref, dtype):
 def test_speed_against_the_reference_kernels(ref):
     """Device time per launch (CUDA events around ten launches on distinct buffers larger than
     L2 in total) of the reference kernel and of the library's, at BASELINE configuration 2's
-    shapes.  Written to gpurun_out/ref_kernel_speedups.txt when that folder exists."""
+    shapes.  Written to ref_kernel_speedups.txt in the run's output folder when that folder exists."""
     from energonai_b200 import kernel as EK
     from energonai_b200.kernel.cuda_native.layer_norm import layer_norm_forward
     rows = []

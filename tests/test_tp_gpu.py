@@ -16,7 +16,7 @@ def _free_port():
 
 
 def _mark(rank, what):
-    """Progress line in gpurun_out/ (when that folder exists): shows how far a rank got if a run
+    """Progress line in the run's output folder (when that folder exists): shows how far a rank got if a run
     has to be ended from outside."""
     out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
     if os.path.isdir(out):
@@ -166,7 +166,7 @@ def _model_worker(rank, world, port, ret, use_peer=False):
                 assert all(torch.equal(both[0], b) for b in both)      # bit-identical on every rank
                 _mark(rank, f"one-shot all-reduce {dt} x {n} ok")
             bad = torch.tensor([float(ctx.peer.status(clear=False)[0] != 0)], device="cuda")
-            dist.all_reduce(bad)                  # agree on the verdict before anybody may leave
+            dist.all_reduce(bad)                  # agree on the outcome before anybody may leave
             assert float(bad) == 0, f"rank {rank}: context status {ctx.peer.status()}"
         model = PipelineModel(vocab_parallel=True, **kw).cuda().eval()
         model.load_state_dict(shard_model_state(full.state_dict(), rank, world, vocab_parallel=True))
