@@ -123,3 +123,27 @@ def test_generation_attention_split_rule():
     assert pick_nsplit(8, 96, 2048) == 1          # 768 (sequence, head) pairs fill the machine already
     assert pick_nsplit(1, 1, 100) == 1
     assert pick_nsplit(1, 1, 1 << 20) == 64
+
+
+def test_attention_and_step_tail_validate_before_any_cuda_call():
+    L = _lib.lib()
+    buf = ctypes.create_string_buffer(64)
+    a = ctypes.addressof(buf) & ~15 or 16
+    # tensor-core prompt attention: head_dim, dtype, strides, scale
+    args = lambda **kw: [kw.get("q", a), a, a, a, None, 8, 8, 8, 8, 8, 8, 8, 8, 0, 1, 1, 8, 8, kw.get("d", 64),
+                         kw.get("causal", 1), kw.get("scale", 0.125), kw.get("dtype", _lib.F16), None]
+    assert L.eb_attention_prefill_tc(*args(d=96)) == -1 and "head_dim" in _lib.last_error()
+    assert L.eb_attention_prefill_tc(*args(dtype=_lib.F32)) == -1 and "fp16 or bf16" in _lib.last_error()
+    assert L.eb_attention_prefill_tc(*args(q=None)) == -1 and "null" in _lib.last_error()
+    assert L.eb_attention_prefill_tc(*args(scale=0.0)) == -1 and "scale" in _lib.last_error()
+    bad = args()
+    bad[6] = 12                       # q row stride not a multiple of 8
+    assert L.eb_attention_prefill_tc(*bad) == -1 and "strides" in _lib.last_error()
+    # the tail of a generation step: sizes and pointers
+    step = lambda **kw: [kw.get("logits", a), kw.get("ld", 16), kw.get("batch", 2), 16, kw.get("dtype", _lib.F16), a, 4, 4, None, a,
+                         kw.get("word", None), 0, 0, None, 0, 1, 0, _lib.F16, None, 0, kw.get("counter", a), None]
+    assert L.eb_greedy_step(*step(batch=0)) == 0
+    assert L.eb_greedy_step(*step(dtype=9)) == -1 and "dtype" in _lib.last_error()
+    assert L.eb_greedy_step(*step(logits=None)) == -1 and "null" in _lib.last_error()
+    assert L.eb_greedy_step(*step(ld=8)) == -1 and "leading" in _lib.last_error()
+    assert L.eb_greedy_step(*step(word=a)) == -1 and "embedding" in _lib.last_error()
